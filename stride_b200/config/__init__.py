@@ -1,0 +1,13 @@
+from .engine import DTYPES, EngineConfig
+from .llama import LlamaConfig
+from .presets import PRESETS, preset
+from .registry import (ConfigError, config_class_for, config_from_dict, load_config, register_architecture,
+                       registered_architectures)
+from .specs import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, RopeScaling, ScheduleEntry,
+                    default_schedule)
+
+__all__ = [
+    "DTYPES", "EngineConfig", "LlamaConfig", "PRESETS", "preset", "ConfigError", "config_class_for", "config_from_dict",
+    "load_config", "register_architecture", "registered_architectures", "FeedForwardSpec", "LayerSpec", "MixerSpec",
+    "ModelSpec", "NormSpec", "PositionSpec", "RopeScaling", "ScheduleEntry", "default_schedule",
+]

@@ -1,0 +1,70 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions
+// and the launch-status convention.
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers, sizes and
+// a stream, validates its sizes on the host and returns 0 or a negative code
+// (-1 bad argument, -2 unsupported size) or a positive cudaError_t. Nothing here
+// allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define STRIDE_DTYPE_F32 0
+#define STRIDE_DTYPE_BF16 1
+
+#define STRIDE_BAD_ARGUMENT (-1)
+#define STRIDE_UNSUPPORTED (-2)
+
+#define STRIDE_LAUNCH_STATUS() static_cast<int>(cudaPeekAtLastError())
+
+namespace stride {
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. The
+// order of the additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = scratch[0];
+    for (int w = 1; w < nwarps; ++w) total = fmaxf(total, scratch[w]);
+    return total;
+}
+
+}  // namespace stride

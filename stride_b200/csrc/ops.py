@@ -1,0 +1,194 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks its tensors (device, dtype, contiguity, sizes) and calls
+one ``extern "C"`` launcher through ctypes on the current torch stream. There is
+no CPU path and no fallback: a tensor that is not on a CUDA device, a missing
+compiler or a size that a kernel refuses raises an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {-1: "bad argument", -2: "size not supported by this kernel"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_bound: dict[str, ctypes._CFuncPtr] = {}
+
+_SIGNATURES = {
+    # name: (library, argtypes)
+    "stride_embed_gather": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_add_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+    "stride_add_residual": ("elementwise", [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
+    "stride_rope_kv_write": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                             c_int, c_int, c_void_p]),
+    "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+}
+
+
+def _fn(name: str):
+    f = _bound.get(name)
+    if f is None:
+        library, argtypes = _SIGNATURES[name]
+        f = getattr(build.load_kernel_library(library), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _bound[name] = f
+    return f
+
+
+def _check(code: int, name: str) -> None:
+    if code == 0:
+        return
+    if code in _ERRORS:
+        raise KernelError(f"{name}: {_ERRORS[code]}")
+    raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device; stride_b200 has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _opt(t, name: str, dtype=None) -> int | None:
+    return None if t is None else _dev(t, name, dtype)
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"element type {dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def require_device() -> None:
+    """Fails loudly when the product path cannot run."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: stride_b200 runs its models on the GPU only")
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(ids, seq_of_token, table, out) -> None:
+    tokens, hidden = out.shape
+    _check(_fn("stride_embed_gather")(_dev(ids, "ids", torch.int32), _opt(seq_of_token, "seq_of_token", torch.int32),
+                                      _dev(table, "table"), _dev(out, "out", torch.float32), tokens, hidden,
+                                      table.shape[0], _code(table.dtype), _stream()), "embed_gather")
+
+
+def add_rmsnorm(residual, delta, weight, out, eps: float, rows=None) -> None:
+    """``x = residual (+ delta)``; writes x back to ``residual`` (unless ``rows``
+    selects source rows) and ``rmsnorm(x) * weight`` to ``out``."""
+    num_rows, hidden = out.shape
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("delta and out must have the same element type")
+    _check(_fn("stride_add_rmsnorm")(_dev(residual, "residual", torch.float32), _opt(delta, "delta"),
+                                     _dev(weight, "weight", torch.float32), _dev(out, "out"),
+                                     _opt(rows, "rows", torch.int32), num_rows, hidden, float(eps), _code(out.dtype),
+                                     _stream()), "add_rmsnorm")
+
+
+def add_residual(residual, delta) -> None:
+    _check(_fn("stride_add_residual")(_dev(residual, "residual", torch.float32), _dev(delta, "delta"), delta.numel(),
+                                      _code(delta.dtype), _stream()), "add_residual")
+
+
+def rope_kv_write(qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages, nq: int, nkv: int, hd: int,
+                  page_size: int, rotate: bool = True) -> None:
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+        raise KernelError("qkv has the wrong width")
+    if k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype:
+        raise KernelError("cache pages and activations must have the same element type")
+    _check(_fn("stride_rope_kv_write")(_dev(qkv, "qkv"), _opt(bias, "bias", torch.float32),
+                                       _dev(positions, "positions", torch.int32),
+                                       _opt(slot_mapping, "slot_mapping", torch.int32), _dev(cos, "cos", torch.float32),
+                                       _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
+                                       tokens, nq, nkv, hd, page_size, int(rotate), _code(qkv.dtype), _stream()),
+           "rope_kv_write")
+
+
+def silu_mul(inp, out) -> None:
+    tokens, inter = out.shape
+    if inp.shape != (tokens, 2 * inter) or inp.dtype != out.dtype:
+        raise KernelError("silu_mul wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
+    _check(_fn("stride_silu_mul")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, _code(out.dtype), _stream()), "silu_mul")
+
+
+# ----------------------------------------------------------------------- matmul
+def linear(x, weight, out) -> None:
+    """``out = x @ weight.T`` for row-major ``weight`` [out_features, in_features].
+
+    float32 runs the package's own FMA kernel (true 32-bit, order of the sum
+    fixed). bfloat16 calls the library matrix product, as the reference's engine
+    does (python/stride_worker/model.py:258-260); ``out`` may then be float32 to
+    keep the accumulator's precision (the output head).
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or out.shape != (m, n):
+        raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
+    if x.dtype == torch.float32:
+        _check(_fn("stride_gemm_nt_f32")(_dev(x, "x", torch.float32), _dev(weight, "weight", torch.float32),
+                                         _dev(out, "out", torch.float32), m, n, k, k, k, n, _stream()), "gemm_nt_f32")
+        return
+    _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out")
+    if m == 0:
+        return
+    if out.dtype == torch.float32:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    else:
+        torch.mm(x, weight.t(), out=out)
+
+
+# -------------------------------------------------------------------- attention
+def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, nq: int, nkv: int,
+                    hd: int, page_size: int, scale: float, window: int = 0) -> None:
+    """Attention of every token in the flat batch over its request's pages.
+    ``q`` holds head h of token t at ``q[t * q_stride + h * hd]``."""
+    tokens = out.shape[0]
+    if out.shape[1] != nq * hd:
+        raise KernelError("attention output has the wrong width")
+    _check(_fn("stride_paged_attention_generic")(
+        _dev(q, "q"), q_stride, _dev(out, "out"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, page_size, float(scale), int(window),
+        _code(q.dtype), _stream()), "paged_attention")
+
+
+# --------------------------------------------------------------------- sampling
+def sample_rows(logits, out, temperature=None, uniform=None, suppress=None) -> None:
+    """Greedy (no ``temperature``, or 0) or temperature sampling per row."""
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("logits rows must be dense")
+    if not logits.is_cuda:
+        raise KernelError("logits must live on a CUDA device; stride_b200 has no CPU path")
+    _check(_fn("stride_sample_rows")(logits.data_ptr(), rows, vocab, logits.stride(0),
+                                     _opt(temperature, "temperature", torch.float32),
+                                     _opt(uniform, "uniform", torch.float32), _opt(suppress, "suppress", torch.int32),
+                                     _dev(out, "out", torch.int32), _stream()), "sample_rows")

@@ -1,0 +1,172 @@
+"""The step function: runs one batch of (request, its next tokens) through the
+model from the cache and returns the logits at the wanted places.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere
+(python/stride_worker/model.py:225-346 is the reference's step). The host packs
+the index arrays once, copies them with one transfer from pinned memory and
+launches the kernels on the current stream. Decode-only batches are padded to a
+bucket size and replayed from a CUDA graph captured for that bucket, which
+removes the launch cost of the several hundred kernels of a step.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from ..csrc.build import load_runtime
+from .context import make_context
+
+
+def _buckets(limit: int) -> list[int]:
+    out, b = [], 1
+    while b < limit:
+        out.append(b)
+        b *= 2
+    out.append(limit)
+    return out
+
+
+class _Staging:
+    """Pinned host buffer + device buffer of one packed layout."""
+
+    def __init__(self, layout: dict, device):
+        self.layout = layout
+        pin = torch.device(device).type == "cuda"
+        self.host = torch.zeros(layout["total"], dtype=torch.int32, pin_memory=pin)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(layout["total"], dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event() if pin else None
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.copied is not None:
+            self.copied.record()
+
+    def wait_host_free(self) -> None:
+        if self.copied is not None:
+            self.copied.synchronize()
+
+
+class ModelRunner:
+    def __init__(self, model, cache_manager, *, token_capacity: int, seq_capacity: int, row_capacity: int,
+                 max_model_len: int, cuda_graphs: bool = True):
+        ops.require_device()
+        self.model = model
+        self.cache = cache_manager
+        self.rt = model.rt
+        self.device = self.rt.device
+        self.groups = cache_manager.num_groups
+        self.token_capacity, self.seq_capacity, self.row_capacity = token_capacity, seq_capacity, row_capacity
+        self.table_width = max(1, cache_manager.pages_for(max_model_len))
+        self._rt_mod = load_runtime()
+        self._eager = _Staging(self._rt_mod.packed_layout(self.groups, token_capacity, seq_capacity, row_capacity,
+                                                          self.table_width), self.device)
+        self.cuda_graphs = cuda_graphs and model.graph_safe
+        self._decode_buckets = _buckets(min(seq_capacity, token_capacity))
+        self._graphs: dict[int, tuple] = {}
+        self.steps = 0
+        self.graph_replays = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ public
+    def step(self, batch, to_host: bool = False):
+        """Runs ``batch`` (a runtime ``StepBatch``). Returns float32 logits
+        [batch.num_rows, vocab] in the order of the wanted places: a view of a
+        reused device buffer, valid until the next step — or a CPU tensor when
+        ``to_host`` is set or the rows exceed the row capacity (they are then
+        produced in slices)."""
+        self.steps += 1
+        if batch.num_tokens == 0:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device="cpu" if to_host else self.device)
+        if batch.num_tokens > self.token_capacity or batch.num_seqs > self.seq_capacity:
+            raise ValueError(f"the step has {batch.num_tokens} tokens of {batch.num_seqs} requests; the runner was sized "
+                             f"for {self.token_capacity} and {self.seq_capacity}")
+        if batch.max_pages > self.table_width:
+            raise ValueError("a request is longer than max_model_len")
+        if self.cuda_graphs and batch.decode_only and batch.num_rows == batch.num_seqs:
+            logits = self._step_graph(batch)
+            return logits.cpu() if to_host else logits
+        return self._step_eager(batch, to_host)
+
+    # ------------------------------------------------------------------- eager
+    def _context(self, staging, batch, num_tokens, num_rows):
+        items, row = [], 0
+        for request, tokens, position, _want in batch.items():
+            items.append((request, row, len(tokens), position, self.cache.state_slot(request)))
+            row += len(tokens)
+        return make_context(staging.dev, staging.layout, num_tokens, batch.num_seqs, num_rows, max_q_len=batch.max_q_len,
+                            max_ctx=batch.max_ctx, decode_only=batch.decode_only, host_items=items)
+
+    def _pack(self, staging, batch):
+        l = staging.layout
+        staging.wait_host_free()
+        batch.pack(self.groups, l["token_cap"], l["seq_cap"], l["row_cap"], l["table_width"], staging.host_np)
+        staging.upload()
+
+    def _step_eager(self, batch, to_host):
+        rows = batch.num_rows
+        if rows <= self.row_capacity:
+            self._pack(self._eager, batch)
+            ctx = self._context(self._eager, batch, batch.num_tokens, rows)
+            logits = self.model.forward(ctx)
+            return logits.cpu() if to_host else logits
+        # More rows wanted than the logits buffer holds: run the layers once and
+        # the head slice by slice, gathering on the host.
+        l = self._eager.layout
+        self._eager.wait_host_free()
+        all_rows = self._wanted_rows(batch)
+        out = torch.empty((rows, self.model.vocab), dtype=torch.float32)
+        stream = None
+        for lo in range(0, rows, self.row_capacity):
+            hi = min(rows, lo + self.row_capacity)
+            if stream is None:
+                batch.pack(self.groups, l["token_cap"], l["seq_cap"], l["row_cap"], l["table_width"], self._eager.host_np,
+                           row_offset=lo, row_count=hi - lo)
+                self._eager.upload()
+                ctx = self._context(self._eager, batch, batch.num_tokens, hi - lo)
+                stream = self.model.forward_layers(ctx)
+            else:
+                ctx.logit_rows[:hi - lo].copy_(torch.as_tensor(all_rows[lo:hi], dtype=torch.int32), non_blocking=False)
+                ctx.num_rows = hi - lo
+            out[lo:hi] = self.model.forward_head(stream, ctx).cpu()
+        return out
+
+    @staticmethod
+    def _wanted_rows(batch):
+        rows, at = [], 0
+        for _request, tokens, _position, want in batch.items():
+            rows.extend(at + w for w in want)
+            at += len(tokens)
+        return rows
+
+    # ------------------------------------------------------------------ graphs
+    def _bucket(self, n: int) -> int:
+        for b in self._decode_buckets:
+            if b >= n:
+                return b
+        return self._decode_buckets[-1]
+
+    def _step_graph(self, batch):
+        b = self._bucket(batch.num_seqs)
+        entry = self._graphs.get(b)
+        if entry is None:
+            staging = _Staging(self._rt_mod.packed_layout(self.groups, b, b, b, self.table_width), self.device)
+            self._pack(staging, batch)
+            ctx = self._context(staging, batch, b, b)
+            self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            entry = (staging, graph, logits)
+            self._graphs[b] = entry
+        staging, graph, logits = entry
+        self._pack(staging, batch)
+        graph.replay()
+        self.graph_replays += 1
+        return logits[:batch.num_rows]
+
+    def captured_buckets(self) -> list[int]:
+        return sorted(self._graphs)

@@ -1,0 +1,87 @@
+"""Grouped-query attention over the paged cache.
+
+q/k/v projections (fused into one matrix product at load time), position
+encoding and cache write, attention of every token over its request's pages,
+output projection: python/stride_worker/model.py:258-299 with the attention rule
+of python/stride_worker/layers.py:109-149. Biases are used when the spec says so.
+A window (not used by Llama 3) limits each token to its last W keys.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import CacheRequest, Mixer, TensorDecl, build_part, register_part
+
+
+class PagedAttention(Mixer):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ValueError(f"{s.num_heads} query heads do not group into {s.num_kv_heads} KV heads")
+        if s.head_dim % 16 or s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim} is not supported by the attention kernels "
+                             "(multiples of 16 up to 256 are)")
+        if s.window is not None and s.window <= 0:
+            raise ValueError("an attention window must be positive")
+        self.hidden = s.hidden
+        self.nq, self.nkv, self.hd = s.num_heads, s.num_kv_heads, s.head_dim
+        self.q_dim, self.kv_dim = self.nq * self.hd, self.nkv * self.hd
+        self.qkv_dim = self.q_dim + 2 * self.kv_dim
+        self.scale = float(s.scale)
+        self.window = 0 if s.window is None else int(s.window)
+        self.position = build_part("position", s.position, runtime)
+        self.w_qkv = self.w_o = self.bias = None
+
+    # ----------------------------------------------------------------- weights
+    def _names(self):
+        p = self.spec.prefix
+        return {k: f"{p}{k}_proj.weight" for k in "qkvo"}, {k: f"{p}{k}_proj.bias" for k in "qkv"}
+
+    def declare(self):
+        w, b = self._names()
+        d = {w["q"]: TensorDecl((self.q_dim, self.hidden)), w["k"]: TensorDecl((self.kv_dim, self.hidden)),
+             w["v"]: TensorDecl((self.kv_dim, self.hidden)), w["o"]: TensorDecl((self.hidden, self.q_dim))}
+        if self.spec.bias:
+            d[b["q"]] = TensorDecl((self.q_dim,), "vector")
+            d[b["k"]] = TensorDecl((self.kv_dim,), "vector")
+            d[b["v"]] = TensorDecl((self.kv_dim,), "vector")
+        return d
+
+    def bind(self, weights):
+        w, b = self._names()
+        self.w_qkv = torch.cat([weights[w["q"]], weights[w["k"]], weights[w["v"]]], dim=0).contiguous()
+        self.w_o = weights[w["o"]]
+        if self.spec.bias:
+            self.bias = torch.cat([weights[b["q"]], weights[b["k"]], weights[b["v"]]]).contiguous()
+
+    def named_tensors(self):
+        w, b = self._names()
+        q, k = self.q_dim, self.q_dim + self.kv_dim
+        out = {w["q"]: self.w_qkv[:q], w["k"]: self.w_qkv[q:k], w["v"]: self.w_qkv[k:], w["o"]: self.w_o}
+        if self.bias is not None:
+            out.update({b["q"]: self.bias[:q], b["k"]: self.bias[q:k], b["v"]: self.bias[k:]})
+        return out
+
+    # ------------------------------------------------------------------- cache
+    def cache_request(self):
+        return CacheRequest(self.nkv, self.hd, self.spec.window)
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, x, ctx, cache):
+        tokens = x.shape[0]
+        qkv = self.rt.buffer("qkv", tokens, self.qkv_dim)
+        ops.linear(x, self.w_qkv, qkv)
+        self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
+        attn = self.rt.buffer("attn", tokens, self.q_dim)
+        ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, ctx.block_table[cache.group],
+                            ctx.seq_of_token[:tokens], ctx.positions[:tokens], self.nq, self.nkv, self.hd,
+                            cache.page_size, self.scale, self.window)
+        out = self.rt.buffer("mixer_out", tokens, self.hidden)
+        ops.linear(attn, self.w_o, out)
+        return out
+
+
+register_part("mixer", "attention", PagedAttention)
