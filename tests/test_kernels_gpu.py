@@ -1,0 +1,322 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same
+operation, at sizes other than the engine's test models (odd widths, a prime
+vocabulary, several head sizes and groupings)."""
+
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1.2e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from stride_b200.csrc import ops as _ops
+    return _ops
+
+
+def dev(t, dtype=None):
+    return t.to(device="cuda", dtype=dtype or t.dtype).contiguous()
+
+
+def close(got, want, dtype, scale=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    scale = scale if scale is not None else float(want.abs().max().clamp_min(1e-6))
+    err = float((got - want).abs().max())
+    assert err <= TOL[dtype] * scale, f"max abs error {err:.3e} against scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(ops, dtype):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(251, 88, generator=g).to(dtype)
+    ids = torch.tensor([0, 250, 17, 17, 3], dtype=torch.int32)
+    seq = torch.tensor([0, 0, 1, -1, 2], dtype=torch.int32)
+    out = torch.full((5, 88), 7.0, device="cuda")
+    ops.embed_gather(dev(ids), dev(seq), dev(table), out)
+    want = table[ids.long()].float()
+    want[3] = 0
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,eps", [(88, 3e-5), (4104, 1e-6), (64, 1e-5)])
+def test_add_rmsnorm(ops, dtype, hidden, eps):
+    g = torch.Generator().manual_seed(2)
+    res = torch.randn(9, hidden, generator=g) * 3
+    delta = (torch.randn(9, hidden, generator=g)).to(dtype)
+    w = 1 + 0.2 * torch.randn(hidden, generator=g)
+    # with delta: residual updated, norm of the sum
+    r = dev(res.clone())
+    out = torch.empty(9, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r, dev(delta), dev(w), out, eps)
+    x = res.double() + delta.double()
+    close(r, x, torch.float32)
+    close(out, plain.rms_norm(x, w.double(), eps), dtype)
+    # without delta: residual untouched
+    r = dev(res.clone())
+    ops.add_rmsnorm(r, None, dev(w), out, eps)
+    assert torch.equal(r.cpu(), res)
+    close(out, plain.rms_norm(res.double(), w.double(), eps), dtype)
+    # gathered rows: residual untouched, only those rows produced
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    r = dev(res.clone())
+    out3 = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r, dev(delta), dev(w), out3, eps, rows=dev(rows))
+    assert torch.equal(r.cpu(), res)
+    close(out3, plain.rms_norm(x[rows.long()], w.double(), eps), dtype)
+
+
+def test_rmsnorm_is_not_fooled_by_a_missing_eps_or_a_mean_over_the_wrong_axis(ops):
+    # negative controls in the manner of python/stride_worker/autotune/negative_control.py
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(4, 96, generator=g) * 1e-3
+    w = torch.ones(96)
+    out = torch.empty(4, 96, device="cuda")
+    ops.add_rmsnorm(dev(x.clone()), None, dev(w), out, 1e-5)
+    good = plain.rms_norm(x.double(), w.double(), 1e-5)
+    no_eps = plain.rms_norm(x.double(), w.double(), 0.0)
+    wrong_axis = x.double() * torch.rsqrt((x.double() ** 2).mean(0, keepdim=True) + 1e-5)
+    err = lambda ref: float((out.cpu().double() - ref).abs().max())
+    assert err(good) < 1e-6 < min(err(no_eps), err(wrong_axis))
+
+
+@pytest.mark.parametrize("m", [1, 7, 65, 130])
+def test_gemm_f32_matches_float64_and_does_not_depend_on_the_batch(ops, m):
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(130, 137, generator=g)
+    w = torch.randn(251, 137, generator=g)
+    out = torch.empty(m, 251, device="cuda")
+    ops.linear(dev(a[:m]), dev(w), out)
+    close(out, a[:m].double() @ w.double().T, torch.float32)
+    full = torch.empty(130, 251, device="cuda")
+    ops.linear(dev(a), dev(w), full)
+    assert torch.equal(full[:m], out), "a row's result changed with the number of rows"
+
+
+def test_linear_bf16(ops):
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(33, 96, generator=g).bfloat16()
+    w = torch.randn(251, 96, generator=g).bfloat16()
+    want = a.double() @ w.double().T
+    out = torch.empty(33, 251, dtype=torch.bfloat16, device="cuda")
+    ops.linear(dev(a), dev(w), out)
+    close(out, want, torch.bfloat16)
+    out32 = torch.empty(33, 251, dtype=torch.float32, device="cuda")
+    ops.linear(dev(a), dev(w), out32)
+    close(out32, want, torch.float32, scale=float(want.abs().max()) * 10)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page,bias", [(5, 5, 48, 16, False), (6, 2, 16, 8, True), (8, 1, 128, 16, False)])
+def test_rope_kv_write(ops, dtype, nq, nkv, hd, page, bias):
+    g = torch.Generator().manual_seed(6)
+    tokens, num_pages, max_pos = 11, 9, 700
+    heads = nq + 2 * nkv
+    qkv = torch.randn(tokens, heads * hd, generator=g).to(dtype)
+    b = torch.randn(heads * hd, generator=g) * 0.1 if bias else None
+    positions = torch.tensor([0, 1, 2, 3, 650, 651, 15, 16, 17, 699, 5], dtype=torch.int32)
+    slots = torch.randperm(num_pages * page, generator=g)[:tokens].to(torch.int32)
+    slots[10] = -1  # a padded token writes nothing
+    scaling = {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 2.0,
+               "original_max_position_embeddings": 32}
+    inv = plain.rope_inv_freq(hd, 25000.0, scaling)
+    angles = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    k_pages = torch.zeros(num_pages, nkv, page, hd, dtype=dtype, device="cuda")
+    v_pages = torch.zeros_like(k_pages)
+    q_dev = dev(qkv.clone())
+    ops.rope_kv_write(q_dev, None if b is None else dev(b), dev(positions), dev(slots), dev(angles.cos()), dev(angles.sin()),
+                      k_pages, v_pages, nq, nkv, hd, page)
+    x = qkv.double().view(tokens, heads, hd)
+    if b is not None:
+        x = x + b.double().view(1, heads, hd)
+    cos, sin = plain.rope_tables(hd, positions, 25000.0, scaling)
+    q_want = plain.apply_rope(x[:, :nq], cos.double(), sin.double())
+    k_want = plain.apply_rope(x[:, nq:nq + nkv], cos.double(), sin.double())
+    v_want = x[:, nq + nkv:]
+    close(q_dev.view(tokens, heads, hd)[:, :nq], q_want, dtype)
+    # values and keys in the pool: only the addressed slots changed
+    k_ref = torch.zeros(num_pages, nkv, page, hd, dtype=torch.float64)
+    v_ref = torch.zeros_like(k_ref)
+    for t in range(tokens):
+        s = int(slots[t])
+        if s >= 0:
+            k_ref[s // page, :, s % page] = k_want[t]
+            v_ref[s // page, :, s % page] = v_want[t]
+    close(k_pages, k_ref, dtype)
+    close(v_pages, v_ref, dtype)
+    # the q part of a padded token is still rotated; untouched columns (k, v in qkv) are not required to change
+    # negative control: the interleaved rotation is a different function
+    inter = x[:, :nq].clone()
+    a, c = inter[..., 0::2], inter[..., 1::2]
+    ch, sh = cos.double()[:, None, :hd // 2], sin.double()[:, None, :hd // 2]
+    wrong = torch.stack([a * ch - c * sh, c * ch + a * sh], -1).flatten(-2)
+    assert float((q_dev.view(tokens, heads, hd)[:, :nq].double().cpu() - wrong).abs().max()) > 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    g = torch.Generator().manual_seed(7)
+    x = (torch.randn(13, 2 * 136, generator=g) * 4).to(dtype)
+    out = torch.empty(13, 136, dtype=dtype, device="cuda")
+    ops.silu_mul(dev(x), out)
+    gate, up = x[:, :136].double(), x[:, 136:].double()
+    close(out, gate * torch.sigmoid(gate) * up, dtype)
+
+
+def _paged_case(g, dtype, seqs, nq, nkv, hd, page, window=None, spike=None):
+    """seqs: list of (context_before, new_tokens). Builds scattered pages that hold
+    the keys and values of every token and returns what the kernel needs together
+    with the plain result for the new tokens."""
+    total_pages = sum(-(-(c + n) // page) for c, n in seqs) + 5
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    k_pages = torch.zeros(total_pages, nkv, page, hd)
+    v_pages = torch.zeros_like(k_pages)
+    width = max(-(-(c + n) // page) for c, n in seqs) + 1
+    table = torch.full((len(seqs), width), -1, dtype=torch.int32)
+    q_rows, pos_rows, seq_rows, want_rows = [], [], [], []
+    for s, (ctx, new) in enumerate(seqs):
+        n = ctx + new
+        q = torch.randn(n, nq, hd, generator=g)
+        k = torch.randn(n, nkv, hd, generator=g)
+        v = torch.randn(n, nkv, hd, generator=g)
+        if spike is not None and n > spike[1]:
+            # one far key gets a score that stands out for one query
+            qi, kj = n - 1, spike[1]
+            k[kj, :] = q[qi].view(nkv, nq // nkv, hd)[:, 0] * 3.0
+        q, k, v = q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float()
+        for p in range(-(-n // page)):
+            page_id = perm.pop()
+            table[s, p] = page_id
+            lo, hi = p * page, min(n, (p + 1) * page)
+            k_pages[page_id, :, :hi - lo] = k[lo:hi].transpose(0, 1)
+            v_pages[page_id, :, :hi - lo] = v[lo:hi].transpose(0, 1)
+        full = plain.causal_attention(q.double(), k.double(), v.double(), hd ** -0.5, window)
+        q_rows.append(q[ctx:])
+        want_rows.append(full[ctx:])
+        pos_rows += list(range(ctx, n))
+        seq_rows += [s] * new
+    q_flat = torch.cat(q_rows).reshape(-1, nq * hd)
+    return (q_flat.to(dtype), k_pages.to(dtype), v_pages.to(dtype), table, torch.tensor(seq_rows, dtype=torch.int32),
+            torch.tensor(pos_rows, dtype=torch.int32), torch.cat(want_rows).reshape(-1, nq * hd))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (5, 5, 48, 16, None), (8, 2, 128, 16, None), (2, 1, 256, 16, None),
+    (4, 2, 64, 8, 5), (4, 4, 32, 16, 40),
+])
+def test_paged_attention(ops, dtype, nq, nkv, hd, page, window):
+    g = torch.Generator().manual_seed(8)
+    # a whole prompt, a portion that starts at a page edge, one in the middle of a page, single decoded tokens
+    seqs = [(0, 37), (32, 9), (45, 2), (130, 1), (16, 1), (0, 1), (63, 1), (64, 1)]
+    q, k_pages, v_pages, table, seq_of, pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, window)
+    # padding rows
+    q = torch.cat([q, torch.zeros(2, nq * hd, dtype=dtype)])
+    seq_of = torch.cat([seq_of, torch.tensor([-1, -1], dtype=torch.int32)])
+    pos = torch.cat([pos, torch.zeros(2, dtype=torch.int32)])
+    out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+    ops.paged_attention(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), nq, nkv, hd,
+                        page, hd ** -0.5, window or 0)
+    close(out[:-2], want, dtype, scale=1.0)
+    assert float(out[-2:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    g = torch.Generator().manual_seed(9)
+    nq, nkv, hd, page = 4, 2, 64, 16
+    seqs = [(699, 1), (0, 700)]
+    q, k_pages, v_pages, table, seq_of, pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, spike=(None, 17))
+    out = torch.empty(q.shape[0], nq * hd, dtype=dtype, device="cuda")
+    ops.paged_attention(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), nq, nkv, hd,
+                        page, hd ** -0.5, 0)
+    close(out, want, dtype, scale=1.0)
+    # the spiked key dominates the first head of each group for the last query: a kernel that skipped key 17 would be far off
+    assert float(want[0].abs().max()) > 0.5
+
+
+def test_attention_f32_is_bitwise_the_same_for_a_token_alone_and_in_a_portion(ops):
+    g = torch.Generator().manual_seed(10)
+    nq, nkv, hd, page = 4, 2, 32, 8
+    q, k_pages, v_pages, table, seq_of, pos, _ = _paged_case(g, torch.float32, [(0, 100)], nq, nkv, hd, page)
+    out = torch.empty(100, nq * hd, device="cuda")
+    args = (dev(k_pages), dev(v_pages), dev(table))
+    ops.paged_attention(dev(q), nq * hd, out, *args, dev(seq_of), dev(pos), nq, nkv, hd, page, hd ** -0.5, 0)
+    for t in (0, 7, 8, 31, 32, 99):
+        one = torch.empty(1, nq * hd, device="cuda")
+        ops.paged_attention(dev(q[t:t + 1]), nq * hd, one, *args, dev(seq_of[t:t + 1]), dev(pos[t:t + 1]), nq, nkv, hd,
+                            page, hd ** -0.5, 0)
+        assert torch.equal(one[0], out[t])
+
+
+def test_kernels_refuse_sizes_they_cannot_run(ops):
+    q = torch.zeros(1, 24, device="cuda")
+    pages = torch.zeros(1, 1, 16, 24, device="cuda")
+    table = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.paged_attention(q, 24, torch.empty(1, 24, device="cuda"), pages, pages, table, z, z, 1, 1, 24, 16, 1.0, 0)
+    with pytest.raises(ops.KernelError, match="CUDA device"):
+        ops.silu_mul(torch.zeros(1, 4), torch.zeros(1, 2))
+
+
+def test_sample_rows_greedy_takes_the_first_maximum_and_honours_suppression(ops):
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(6, 1003, generator=g)
+    logits[0, 5] = logits[0, 900] = 9.0          # a tie: the lower index wins
+    logits[1, 1002] = 9.0                        # the last column
+    logits[2, 0] = 9.0
+    logits[3, 77] = 9.0                          # suppressed below
+    logits[3, 78] = 8.0
+    logits[4] = float("-inf")
+    logits[4, 400] = -3.0
+    suppress = torch.tensor([-1, -1, -1, 77, -1, -1], dtype=torch.int32)
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(logits), out, suppress=dev(suppress))
+    want = [plain.sample(logits[r], plain.XorShiftRng(0), temperature=0.0, eos=int(suppress[r]) if suppress[r] >= 0 else None,
+                         min_tokens=1, generated=0) for r in range(6)]
+    assert out.tolist() == want == [5, 1002, 0, 78, 400, int(logits[5].argmax())]
+
+
+def test_sample_rows_draws_from_the_softmax(ops):
+    g = torch.Generator().manual_seed(12)
+    vocab = 1003
+    logits = torch.randn(1, vocab, generator=g) * 2
+    t = 0.7
+    probs = torch.softmax(logits[0].double() / t, 0)
+    cdf = torch.cumsum(probs, 0)
+    n = 4096
+    u = torch.rand(n, generator=g)
+    rows = logits.expand(n, vocab).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(rows), out, temperature=dev(torch.full((n,), t)), uniform=dev(u))
+    got = out.cpu().long()
+    want = torch.searchsorted(cdf, u.double()).clamp(max=vocab - 1)
+    # the same inverse-CDF rule; rounding may move a draw that falls within 1e-5 of a boundary
+    boundary_gap = (cdf[want] - u.double()).abs().minimum((cdf[(want - 1).clamp(min=0)] - u.double()).abs())
+    differs = got != want
+    assert int((differs & (boundary_gap > 1e-5)).sum()) == 0
+    assert float(differs.float().mean()) < 0.01
+    # and the frequencies follow the distribution
+    top = int(probs.argmax())
+    assert abs(float((got == top).float().mean()) - float(probs[top])) < 0.03
+    # temperature 0 inside the same call is greedy; a suppressed token is never drawn
+    mixed_t = torch.tensor([0.0, 1.0], dtype=torch.float32)
+    two = logits.expand(2, vocab).contiguous()
+    out2 = torch.empty(2, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(two), out2, temperature=dev(mixed_t), uniform=dev(torch.tensor([0.5, 0.5])),
+                    suppress=dev(torch.tensor([-1, top], dtype=torch.int32)))
+    assert out2[0].item() == top and out2[1].item() != top
+    uniform_logits = torch.full((1, 10), float("-inf"))
+    out1 = torch.empty(1, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(uniform_logits), out1, temperature=dev(torch.ones(1)), uniform=dev(torch.tensor([0.35])))
+    assert out1.item() == 3
