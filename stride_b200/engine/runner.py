@@ -68,7 +68,7 @@ class ModelRunner:
         self._graphs: dict[int, tuple] = {}
         self.steps = 0
         self.graph_replays = 0
-        self.kernel_launches = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ public
     def step(self, batch, to_host: bool = False):
@@ -104,6 +104,7 @@ class ModelRunner:
         staging.wait_host_free()
         batch.pack(self.groups, l["token_cap"], l["seq_cap"], l["row_cap"], l["table_width"], staging.host_np)
         staging.upload()
+        self.last_h2d_bytes = l["total"] * 4
 
     def _step_eager(self, batch, to_host):
         rows = batch.num_rows
