@@ -75,6 +75,16 @@ def find_nvcc() -> str:
     return found
 
 
+def find_cxx() -> str:
+    """The host compiler: ``$STRIDE_B200_CXX``, else the system's g++ (a wrapper
+    named by ``$CXX`` may link libstdc++ statically, which breaks exceptions and
+    streams in a module loaded beside torch), else ``$CXX``."""
+    for candidate in (os.environ.get("STRIDE_B200_CXX"), shutil.which("g++"), shutil.which("c++"), os.environ.get("CXX")):
+        if candidate:
+            return candidate
+    raise BuildError("no C++ compiler found (g++, c++ or $CXX)")
+
+
 def _digest(paths: list[str], flags: list[str]) -> str:
     h = hashlib.sha256()
     for p in sorted(paths):
@@ -157,7 +167,7 @@ def build_runtime() -> str:
     suffix_free_includes = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", RUNTIME_DIR]
 
     def cmd(out):
-        return [os.environ.get("CXX", "g++"), *CXX_FLAGS, *suffix_free_includes, "-o", out, src]
+        return [find_cxx(), *CXX_FLAGS, *suffix_free_includes, "-o", out, src]
 
     return _build("_runtime", [src], _headers(RUNTIME_DIR), cmd)
 

@@ -246,7 +246,10 @@ public:
     // For the negative control of the invariant check only.
     void corrupt_for_test(int what) {
         if (what == 0 && !free_.empty()) free_.pop_back();          // a page is lost
-        if (what == 1 && !free_.empty()) free_.push_back(free_[0]);  // a page is held twice
+        if (what == 1 && !free_.empty()) {                           // a page is held twice
+            PageId dup = free_[0];
+            free_.push_back(dup);
+        }
         if (what == 2) ++live_;                                      // the counter drifts
     }
 
