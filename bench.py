@@ -1,0 +1,369 @@
+"""Measures decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of Llama-3.1-8B with random bfloat16 weights,
+a batch of 8 requests at a context of 8192 tokens. It prints ONE JSON line:
+
+* ``value``: decoded tokens a second, K decode steps replayed from the captured
+  CUDA graph and timed on the device with CUDA events (the step reads every
+  weight and the whole cache of the live requests, far more than the L2 holds);
+* ``e2e``: the same through the Python entry point (``Engine.step``): host token
+  ids in through pinned memory, scheduling, the step, sampling on the device,
+  token ids back to the host, every step;
+* ``prefill``: one 2,048-token prompt, tokens a second and the fraction of the
+  bf16 matrix peak;
+* ``roofline``: bytes the decode step has to read divided by its time, against
+  the measured copy bandwidth;
+* ``points``: decode at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json when the file exists, else from an earlier
+measurement on the same pool (6.65 TB/s, 1.59 PFLOP/s). ``--impl reference``
+runs the unmodified reference (``baseline/_ref``) on the same shapes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
+                    "source": "measured"}
+        except (ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", "0",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.summary = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": mx, "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------ shapes
+def bench_config(layers: int | None):
+    from stride_b200.config import config_from_dict, preset
+
+    d = preset("llama3.1-8b")
+    full_layers = d["num_hidden_layers"]
+    if layers:
+        d["num_hidden_layers"] = layers
+    return config_from_dict(d), full_layers
+
+
+def decode_bytes(cfg, batch: int, context: int, itemsize: int = 2) -> int:
+    """Bytes a decode step has to read: every matrix once (the embedding table
+    is only gathered from) and the keys and values of the live requests."""
+    matrices = cfg.params_per_layer() * cfg.num_hidden_layers + cfg.vocab_size * cfg.hidden_size
+    return matrices * itemsize + batch * context * cfg.kv_bytes_per_token(itemsize)
+
+
+def prefill_flops(cfg, tokens: int, rows: int = 1) -> float:
+    linear = 2.0 * tokens * cfg.params_per_layer() * cfg.num_hidden_layers + 2.0 * rows * cfg.hidden_size * cfg.vocab_size
+    attention = cfg.num_hidden_layers * 4.0 * cfg.num_attention_heads * cfg.head_dim * tokens * (tokens + 1) / 2
+    return linear + attention
+
+
+# -------------------------------------------------------------------------- ours
+def _synthetic_decode_batch(engine, batch: int, context: int, first_key: int):
+    """``batch`` requests that hold ``context - 1`` tokens in the cache (pages
+    allocated through the cache manager; contents are whatever the pool holds)
+    and bring their next token."""
+    import torch
+
+    rt = engine._rt
+    g = torch.Generator().manual_seed(batch)
+    step = rt.StepBatch(engine.cache)
+    keys = []
+    for i in range(batch):
+        key = first_key + i
+        engine.cache.open(key, "bench")
+        if not engine.cache.ensure(key, context, 0):
+            raise RuntimeError("the page pool is too small for the benchmark batch")
+        step.add(key, [int(torch.randint(0, engine.model.vocab, (1,), generator=g))], context - 1, [0])
+        keys.append(key)
+    return step, keys
+
+
+def _time_graph(engine, step_batch, steps: int, warmup: int):
+    """Device time of ``steps`` replays of the decode graph for this batch."""
+    import torch
+
+    runner = engine.runner
+    for _ in range(max(warmup, 3)):
+        runner.step(step_batch)
+    torch.cuda.synchronize()
+    launches_before = runner.replayed_launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            runner.step(step_batch)
+        end.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    return ms / steps, clocks.summary, runner.replayed_launches - launches_before
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from stride_b200 import Engine, SamplingParams
+    from stride_b200.csrc import ops
+
+    pk = peaks()
+    cfg, full_layers = bench_config(args.layers)
+    batch, context, prompt_len = args.batch, args.context, 2048
+    page = 16
+    need_tokens = max(64 * (context + 64), batch * (context + 256)) + 4096
+    engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=page, num_blocks=need_tokens // page + 64,
+                    max_batch_tokens=2048, max_batch_seqs=64, max_model_len=context + 512, prefix_caching=False,
+                    check_invariants=False)
+    for pages in engine.device_cache.pages:      # synthetic cache contents: small random keys and values
+        pages.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+
+    # ---- prefill: one 2,048-token prompt, device-timed
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist()
+    times = []
+    for i in range(3 + 5):
+        key = 900000 + i
+        engine.cache.open(key, "bench")
+        engine.cache.ensure(key, prompt_len, 0)
+        sb = engine._rt.StepBatch(engine.cache)
+        sb.add(key, prompt, 0, [prompt_len - 1])
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.runner.step(sb)
+        end.record()
+        torch.cuda.synchronize()
+        engine.cache.close(key)
+        if i >= 3:
+            times.append(start.elapsed_time(end))
+    prefill_ms = statistics.median(times)
+    prefill = {"value": round(prompt_len / prefill_ms * 1e3, 1), "tokens": prompt_len, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode points, device-timed graph replays on synthetic caches
+    points, key_base = {}, 1000
+    main = None
+    for b in (1, 64, batch):
+        sb, keys = _synthetic_decode_batch(engine, b, context, key_base)
+        key_base += 1000
+        ms, clocks, launches = _time_graph(engine, sb, args.steps, args.warmup)
+        for k in keys:
+            engine.cache.close(k)
+        if b == batch:
+            main = (ms, clocks, launches)
+        if b in (1, 64):
+            points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
+    ms_per_step, clocks, launches = main
+    value = batch / ms_per_step * 1e3
+    achieved = decode_bytes(cfg, batch, context) / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the entry point: real prompts, scheduling, sampling, host tokens in and out
+    e2e = None
+    if not args.no_e2e:
+        prompts = [torch.randint(0, cfg.vocab_size, (context - 1,), generator=g).tolist() for _ in range(batch)]
+        params = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 8, ignore_eos=True)
+        ids = [engine.add_request(p, params) for p in prompts]
+        while engine.scheduler.num_waiting or any(engine.scheduler.sequence(engine._seq_of_request[i]).state != engine._rt.SeqState.Decoding
+                                                  for i in ids):
+            engine.step()
+        for _ in range(max(args.warmup, 3)):
+            engine.step()
+        h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        for _ in range(args.steps):
+            produced += sum(1 for _rid, tok, _why in engine.step() if tok is not None)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+        e2e = {"value": round(produced / elapsed, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // args.steps,
+               "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // args.steps}
+        launches += 0
+        for i in ids:
+            engine.cancel(i)
+
+    return {
+        "metric": "Llama-3.1-8B decode tok/s at batch 8, context 8192 (bf16, one B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), uniform token ids, random cache contents)",
+        "impl": "ours",
+        "config": {"model": "llama-3.1-8b-shape", "layers": cfg.num_hidden_layers, "layers_of_named_config": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": batch, "seq_len": context, "page_size": page, "prefill_tokens": prompt_len,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights + cache read every step)",
+                   "peaks": pk["source"], "hbm_peak_gbs": pk["hbm_gbs"], "bf16_peak_tflops": pk["bf16_tflops"]},
+        "e2e": e2e, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clocks, "gpu_launches": launches,
+    }
+
+
+# --------------------------------------------------------------------- reference
+def run_reference(args) -> dict:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "stride_worker")):
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no stride_worker package (the offline install was not done here)"}
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from stride_worker.cache import PagedKVCache
+        from stride_worker.model import StrideModel
+        from stride_worker.protocol import SequenceWork
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"the reference does not import: {type(e).__name__}: {e}"[:300]}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+
+    from stride_b200.config import preset
+    d = preset("llama3.1-8b")
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    dev, dt = torch.device("cuda"), torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    H, I, V, L = d["hidden_size"], d["intermediate_size"], d["vocab_size"], d["num_hidden_layers"]
+    q, kv = d["num_attention_heads"] * d["head_dim"], d["num_key_value_heads"] * d["head_dim"]
+
+    def mat(r, c):
+        return (torch.randn(r, c, generator=g, device=dev, dtype=torch.float32) * 0.02).to(dt)
+
+    state = {"model.embed_tokens.weight": mat(V, H), "model.norm.weight": torch.ones(H, device=dev, dtype=dt),
+             "lm_head.weight": mat(V, H)}
+    for i in range(L):
+        p = f"model.layers.{i}"
+        state.update({f"{p}.input_layernorm.weight": torch.ones(H, device=dev, dtype=dt),
+                      f"{p}.post_attention_layernorm.weight": torch.ones(H, device=dev, dtype=dt),
+                      f"{p}.self_attn.q_proj.weight": mat(q, H), f"{p}.self_attn.k_proj.weight": mat(kv, H),
+                      f"{p}.self_attn.v_proj.weight": mat(kv, H), f"{p}.self_attn.o_proj.weight": mat(H, q),
+                      f"{p}.mlp.gate_proj.weight": mat(I, H), f"{p}.mlp.up_proj.weight": mat(I, H),
+                      f"{p}.mlp.down_proj.weight": mat(H, I)})
+    model = StrideModel(d, state, dev, dt)
+    batch, context, page = args.batch, args.context, 16
+    pages_per_seq = (context + page - 1) // page + 1
+    cache = PagedKVCache(model.cache_spec(batch * pages_per_seq + 4, page))
+    tokens = torch.randint(0, V, (batch,), generator=torch.Generator().manual_seed(1)).tolist()
+    work = [SequenceWork(seq=i, tokens=[tokens[i]], position=context - 1,
+                         blocks=list(range(i * pages_per_seq, (i + 1) * pages_per_seq)), needs_logits=True) for i in range(batch)]
+    for _ in range(max(args.warmup, 3)):
+        model.forward(work, cache)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        start.record()
+        produced = 0
+        for _ in range(args.steps):
+            _, logits, _ = model.forward(work, cache)
+            produced += len(logits.to("cpu", torch.float32).argmax(-1).tolist())   # host tokens out, as its worker returns logits
+        end.record()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+    ms = start.elapsed_time(end) / args.steps
+    prompt = torch.randint(0, V, (2048,), generator=torch.Generator().manual_seed(2)).tolist()
+    pw = [SequenceWork(seq=0, tokens=prompt, position=0, blocks=list(range(2048 // page)), needs_logits=True)]
+    model.forward(pw, cache)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    model.forward(pw, cache)
+    torch.cuda.synchronize()
+    prefill_ms = (time.perf_counter() - t1) * 1e3
+    return {"metric": "Llama-3.1-8B decode tok/s at batch 8, context 8192 (bf16, one B200)", "impl": "reference",
+            "value": round(batch / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, zeroed cache)",
+            "config": {"model": "llama-3.1-8b-shape", "layers": L, "global_batch": batch, "seq_len": context,
+                       "page_size": page, "parallelism": "single-gpu"},
+            "e2e": {"value": round(produced / elapsed, 1), "unit": "tokens/s", "h2d_bytes_per_step": batch * 16,
+                    "d2h_bytes_per_step": batch * V * 4},
+            "prefill": {"value": round(2048 / prefill_ms * 1e3, 1), "tokens": 2048, "ms": round(prefill_ms, 2)},
+            "clocks": clocks.summary, "gpu_launches": 0}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (reported in config)")
+    p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    args = p.parse_args(argv)
+    if args.gpus != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not measured"}))
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -53,8 +53,14 @@ def _fn(name: str):
     return f
 
 
+# How many of the package's own kernels were launched (library matrix products
+# are not counted). A captured graph counts its launches once, at capture.
+counters = {"launches": 0}
+
+
 def _check(code: int, name: str) -> None:
     if code == 0:
+        counters["launches"] += 1
         return
     if code in _ERRORS:
         raise KernelError(f"{name}: {_ERRORS[code]}")

@@ -69,6 +69,8 @@ class ModelRunner:
         self.steps = 0
         self.graph_replays = 0
         self.last_h2d_bytes = 0
+        self.launches_per_graph: dict[int, int] = {}
+        self.replayed_launches = 0      # own kernels run through graph replays
 
     # ------------------------------------------------------------------ public
     def step(self, batch, to_host: bool = False):
@@ -159,14 +161,17 @@ class ModelRunner:
             self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            before = ops.counters["launches"]
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
+            self.launches_per_graph[b] = ops.counters["launches"] - before
             entry = (staging, graph, logits)
             self._graphs[b] = entry
         staging, graph, logits = entry
         self._pack(staging, batch)
         graph.replay()
         self.graph_replays += 1
+        self.replayed_launches += self.launches_per_graph[b]
         return logits[:batch.num_rows]
 
     def captured_buckets(self) -> list[int]:
