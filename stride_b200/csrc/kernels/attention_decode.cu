@@ -1,0 +1,301 @@
+// Decode attention in bfloat16 over the paged cache, split over the keys.
+//
+// A decoded token reads every key of its request, so the step is bound by the
+// memory bandwidth; with few requests there are too few (request, head) pairs to
+// fill 148 SMs. The keys are therefore cut into splits of 128: one CTA handles
+// (split, key head, token), multiplies the whole query group of that key head
+// (nq / nkv heads, padded to the 16 rows of an m16n8k16 tile) with its keys on
+// the tensor cores, keeps an online softmax in float32, and writes an
+// unnormalised partial result. A second kernel merges the splits of each
+// (token, query head). All loads of a CTA are issued at once with cp.async, each
+// warp fetching exactly the 32 keys and values it works on, so several CTAs per
+// SM keep enough bytes in flight without a staged pipeline.
+//
+// The rule is that of python/stride_worker/layers.py:109-149 for a single query
+// at position p: keys j <= p (and j > p - window), softmax(q k^T * scale) v, query
+// head h reading key head h / (nq / nkv). Scratch: part_o[token][head][split][hd]
+// and part_ml[token][head][split][2] (running maximum in the log2 domain, sum).
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace stride {
+
+constexpr int kSplitKeys = 128;   // keys per CTA
+constexpr int kWarpKeys = 32;     // keys per warp
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
+                          const __nv_bfloat16* __restrict__ v_pages, const int32_t* __restrict__ block_table,
+                          int table_width, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions,
+                          float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int page_size,
+                          float scale_log2e, int window, int num_splits) {
+    constexpr int ROW_BYTES = HD * 2;
+    constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
+    constexpr int KSTEPS = HD / 16;
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int seq = seq_of_token[t];
+    if (seq < 0) return;
+    const int pos = positions[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = split * kSplitKeys;
+    if (lo > pos || lo + kSplitKeys <= first) return;   // uniform for the CTA
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tg = lane & 3;
+    const int group = nq / nkv;
+    const int wlo = lo + warp * kWarpKeys;
+    const bool warp_valid = !(wlo > pos || wlo + kWarpKeys <= first);
+    const int32_t* table = block_table + static_cast<size_t>(seq) * table_width;
+    unsigned char* ks = smem + warp * kWarpKeys * ROW_BYTES;
+    unsigned char* vs = smem + kSplitKeys * ROW_BYTES + warp * kWarpKeys * ROW_BYTES;
+
+    if (warp_valid) {
+#pragma unroll
+        for (int i = 0; i < kWarpKeys * CHUNKS / 32; ++i) {
+            const int idx = i * 32 + lane;
+            const int row = idx / CHUNKS, c = idx % CHUNKS;
+            const int key = wlo + row;
+            const uint32_t off = swizzled<ROW_BYTES>(row, c);
+            if (key >= first && key <= pos) {
+                const int page = table[key / page_size];
+                const size_t src = ((static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size) * HD + c * 8;
+                cp_async_16(ks + off, k_pages + src);
+                cp_async_16(vs + off, v_pages + src);
+            } else {   // masked keys: zeros, so that 0 * value stays 0
+                *reinterpret_cast<uint4*>(ks + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+    }
+
+    // The query group as the A operand: row r is query head kvh * group + r.
+    uint32_t qa[KSTEPS][4];
+    {
+        const __nv_bfloat16* q_tok = q + static_cast<size_t>(t) * q_stride + static_cast<size_t>(kvh) * group * HD;
+        const bool r0 = g < group, r1 = g + 8 < group;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            const int d = kk * 16 + 2 * tg;
+            qa[kk][0] = r0 ? *reinterpret_cast<const uint32_t*>(q_tok + g * HD + d) : 0u;
+            qa[kk][1] = r1 ? *reinterpret_cast<const uint32_t*>(q_tok + (g + 8) * HD + d) : 0u;
+            qa[kk][2] = r0 ? *reinterpret_cast<const uint32_t*>(q_tok + g * HD + d + 8) : 0u;
+            qa[kk][3] = r1 ? *reinterpret_cast<const uint32_t*>(q_tok + (g + 8) * HD + d + 8) : 0u;
+        }
+    }
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    if (warp_valid) {
+        cp_async_wait<0>();
+        __syncwarp();
+        const uint32_t ks_addr = smem_addr(ks), vs_addr = smem_addr(vs);
+        const int lm = lane >> 3, lr = lane & 7;     // ldmatrix: matrix index and row within it
+#pragma unroll
+        for (int tile = 0; tile < kWarpKeys / 16; ++tile) {
+            const int tlo = wlo + tile * 16;
+            if (tlo > pos || tlo + 16 <= first) continue;
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                uint32_t b[4];
+                ldmatrix_x4(b, ks_addr + swizzled<ROW_BYTES>(tile * 16 + (lm >> 1) * 8 + lr, kk * 2 + (lm & 1)));
+                mma_bf16_16816(s[0], qa[kk], b[0], b[1]);
+                mma_bf16_16816(s[1], qa[kk], b[2], b[3]);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = tlo + nt * 8 + 2 * tg + (e & 1);
+                    const bool ok = key >= first && key <= pos;
+                    s[nt][e] = ok ? s[nt][e] * scale_log2e : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m[r], mx[r]);     // finite: the tile holds at least one allowed key
+                corr[r] = exp2f(m[r] - m_new);
+                m[r] = m_new;
+                l[r] *= corr[r];
+            }
+            uint32_t pa[4];
+            {
+                float p[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        p[nt][e] = exp2f(s[nt][e] - m[e >> 1]);
+                        l[e >> 1] += p[nt][e];
+                    }
+                pa[0] = pack_bf16(p[0][0], p[0][1]);
+                pa[1] = pack_bf16(p[0][2], p[0][3]);
+                pa[2] = pack_bf16(p[1][0], p[1][1]);
+                pa[3] = pack_bf16(p[1][2], p[1][3]);
+            }
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int dn = 0; dn < HD / 16; ++dn) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vs_addr + swizzled<ROW_BYTES>(tile * 16 + (lm & 1) * 8 + lr, dn * 2 + (lm >> 1)));
+                mma_bf16_16816(o[2 * dn], pa, b[0], b[1]);
+                mma_bf16_16816(o[2 * dn + 1], pa, b[2], b[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+
+    // Merge the four warps through shared memory (the key and value tiles are no longer needed).
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem);
+    constexpr int RS = HD + 2;          // per row: hd accumulators, maximum, sum
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+        if (row < group) {
+            float* dst = red + (warp * group + row) * RS;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                dst[i * 8 + 2 * tg] = o[i][2 * r];
+                dst[i * 8 + 2 * tg + 1] = o[i][2 * r + 1];
+            }
+            if (tg == 0) {
+                dst[HD] = m[r];
+                dst[HD + 1] = l[r];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+        const int row = idx / HD, d = idx - row * HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * group + row) * RS + HD]);
+        float acc = 0.f, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = red + (w * group + row) * RS;
+            const float f = exp2f(src[HD] - mm);     // a warp without keys has maximum -inf and weight 0
+            acc += f * src[d];
+            sum += f * src[HD + 1];
+        }
+        const size_t slot = (static_cast<size_t>(t) * nq + kvh * group + row) * num_splits + split;
+        part_o[slot * HD + d] = acc;
+        if (d == 0) {
+            part_ml[slot * 2] = mm;
+            part_ml[slot * 2 + 1] = sum;
+        }
+    }
+}
+
+// out[t, head, :] = sum_s w_s * part_o[s] / sum_s w_s * part_l[s], w_s = 2^(m_s - max m).
+template <int HD>
+__global__ void __launch_bounds__(HD)
+paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                          __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
+                          const int32_t* __restrict__ positions, int nq, int window, int num_splits) {
+    const int head = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(t) * nq + head) * HD;
+    if (seq_of_token[t] < 0) {
+        dst[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = positions[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = first / kSplitKeys, s_hi = pos / kSplitKeys;
+    const size_t base = (static_cast<size_t>(t) * nq + head) * num_splits;
+    float mm = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    float acc = 0.f, sum = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+        const float f = exp2f(part_ml[(base + s) * 2] - mm);
+        acc += f * part_o[(base + s) * HD + d];
+        sum += f * part_ml[(base + s) * 2 + 1];
+    }
+    dst[d] = __float2bfloat16_rn(acc / sum);
+}
+
+template <int HD>
+int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
+                  const __nv_bfloat16* v_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
+                  const int32_t* positions, float* part_o, float* part_ml, int tokens, int nq, int nkv, int page_size,
+                  float scale, int window, int num_splits, cudaStream_t stream) {
+    const int smem = 2 * kSplitKeys * HD * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid(num_splits, nkv, tokens);
+    paged_decode_split_kernel<HD><<<grid, 128, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width,
+                                                               seq_of_token, positions, part_o, part_ml, nq, nkv, page_size,
+                                                               scale * 1.4426950408889634f, window, num_splits);
+    paged_decode_merge_kernel<HD><<<dim3(nq, tokens), HD, 0, stream>>>(part_o, part_ml, out, seq_of_token, positions, nq,
+                                                                       window, num_splits);
+    return STRIDE_LAUNCH_STATUS();
+}
+
+}  // namespace stride
+
+using namespace stride;
+
+extern "C" {
+
+// Number of float32 scratch elements the launcher needs for these sizes.
+long long stride_paged_decode_scratch_floats(int tokens, int nq, int hd, int max_context) {
+    const long long splits = (max_context + kSplitKeys - 1) / kSplitKeys;
+    return static_cast<long long>(tokens) * nq * splits * (hd + 2);
+}
+
+// One query token per entry of the flat batch (decode). Returns -2 for sizes it
+// does not run (head sizes other than 64 and 128, groups above 16, more than
+// 65535 tokens); the caller then uses the generic kernel.
+int stride_paged_decode_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                  const int32_t* block_table, int table_width, const int32_t* seq_of_token,
+                                  const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
+                                  int nkv, int hd, int page_size, float scale, int window, int max_context,
+                                  cudaStream_t stream) {
+    if (tokens < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || max_context <= 0)
+        return STRIDE_BAD_ARGUMENT;
+    if (nq % nkv) return STRIDE_BAD_ARGUMENT;
+    if ((hd != 64 && hd != 128) || nq / nkv > 16 || tokens > 65535 || nkv > 65535 || q_stride % 2) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    const int num_splits = (max_context + kSplitKeys - 1) / kSplitKeys;
+    const long long need = stride_paged_decode_scratch_floats(tokens, nq, hd, max_context);
+    if (scratch == nullptr || scratch_floats < need) return STRIDE_BAD_ARGUMENT;
+    float* part_o = scratch;
+    float* part_ml = scratch + static_cast<long long>(tokens) * nq * num_splits * hd;
+    auto qp = static_cast<const __nv_bfloat16*>(q);
+    auto op = static_cast<__nv_bfloat16*>(out);
+    auto kp = static_cast<const __nv_bfloat16*>(k_pages);
+    auto vp = static_cast<const __nv_bfloat16*>(v_pages);
+    if (hd == 64)
+        return launch_decode<64>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
+                                 tokens, nq, nkv, page_size, scale, window, num_splits, stream);
+    return launch_decode<128>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
+                              tokens, nq, nkv, page_size, scale, window, num_splits, stream);
+}
+
+}  // extern "C"

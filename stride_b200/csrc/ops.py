@@ -38,6 +38,12 @@ _SIGNATURES = {
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                                              c_int, c_int, c_void_p]),
+    "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                           c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
+                                                           c_float, c_int, c_int, c_void_p]),
+    "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                             c_int, c_float, c_int, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
@@ -184,6 +190,48 @@ def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(positions, "positions", torch.int32), tokens, nq, nkv, hd, page_size, float(scale), int(window),
         _code(q.dtype), _stream()), "paged_attention")
+
+
+DECODE_SPLIT_KEYS = 128
+
+
+def fast_attention_supported(dtype, nq: int, nkv: int, hd: int) -> bool:
+    """Sizes that the tensor-core attention kernels run; others use the generic kernel."""
+    return dtype == torch.bfloat16 and hd in (64, 128) and nq % nkv == 0 and nq // nkv <= 16
+
+
+def decode_scratch_floats(tokens: int, nq: int, hd: int, max_context: int) -> int:
+    return tokens * nq * (-(-max_context // DECODE_SPLIT_KEYS)) * (hd + 2)
+
+
+def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,
+                           nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int) -> None:
+    """Attention for single decoded tokens (one query per row), split over the keys;
+    ``scratch`` (float32) holds the partial results of the splits."""
+    tokens = out.shape[0]
+    if out.shape[1] != nq * hd:
+        raise KernelError("attention output has the wrong width")
+    _check(_fn("stride_paged_decode_attention")(
+        _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
+        int(max_context), _stream()), "paged_attention_decode")
+    counters["launches"] += 1       # the launcher runs two kernels
+
+
+def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
+                            nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int) -> None:
+    """Attention for the first ``num_seqs`` requests of the step (portions of any
+    length), which own the rows of ``out``."""
+    tokens = out.shape[0]
+    if out.shape[1] != nq * hd:
+        raise KernelError("attention output has the wrong width")
+    _check(_fn("stride_paged_prefill_attention")(
+        _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32), _dev(ctx_len, "ctx_len", torch.int32),
+        num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window), _stream()), "paged_attention_prefill")
 
 
 # --------------------------------------------------------------------- sampling

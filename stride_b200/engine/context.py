@@ -31,6 +31,16 @@ class StepContext:
     max_q_len: int = 0
     max_ctx: int = 0
     decode_only: bool = False
+    # Requests are laid out in the order given; the trailing run of single-token
+    # requests (decodes) starts at flat row ``decode_tail_start`` and is made of
+    # the sequences from ``decode_tail_seq`` on. Kernels specialised for decode
+    # take that tail, kernels for portions take what comes before it.
+    decode_tail_start: int = 0
+    decode_tail_seq: int = 0
+    # Upper bound of ctx_len that holds for as long as this context's launches
+    # may be replayed (the longest context of the step, or of any step for a
+    # captured graph).
+    context_bound: int = 0
     # Host copy of the step's items for parts that loop in Python:
     # (request, first flat row, number of tokens, position of the first token, state slot)
     host_items: list = field(default_factory=list)

@@ -93,13 +93,20 @@ class ModelRunner:
         return self._step_eager(batch, to_host)
 
     # ------------------------------------------------------------------- eager
-    def _context(self, staging, batch, num_tokens, num_rows):
+    def _context(self, staging, batch, num_tokens, num_rows, for_graph=False):
         items, row = [], 0
         for request, tokens, position, _want in batch.items():
             items.append((request, row, len(tokens), position, self.cache.state_slot(request)))
             row += len(tokens)
+        tail_seq = len(items)
+        while tail_seq > 0 and items[tail_seq - 1][2] == 1:
+            tail_seq -= 1
+        tail_start = items[tail_seq][1] if tail_seq < len(items) else row
+        bound = self.table_width * self.cache.page_size if for_graph else batch.max_ctx
         return make_context(staging.dev, staging.layout, num_tokens, batch.num_seqs, num_rows, max_q_len=batch.max_q_len,
-                            max_ctx=batch.max_ctx, decode_only=batch.decode_only, host_items=items)
+                            max_ctx=batch.max_ctx, decode_only=batch.decode_only, host_items=items,
+                            decode_tail_start=0 if for_graph else tail_start, decode_tail_seq=0 if for_graph else tail_seq,
+                            context_bound=bound)
 
     def _pack(self, staging, batch):
         l = staging.layout
@@ -157,7 +164,7 @@ class ModelRunner:
         if entry is None:
             staging = _Staging(self._rt_mod.packed_layout(self.groups, b, b, b, self.table_width), self.device)
             self._pack(staging, batch)
-            ctx = self._context(staging, batch, b, b)
+            ctx = self._context(staging, batch, b, b, for_graph=True)
             self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()

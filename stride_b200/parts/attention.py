@@ -34,6 +34,7 @@ class PagedAttention(Mixer):
         self.window = 0 if s.window is None else int(s.window)
         self.position = build_part("position", s.position, runtime)
         self.w_qkv = self.w_o = self.bias = None
+        self._fast = ops.fast_attention_supported(runtime.dtype, self.nq, self.nkv, self.hd)
 
     # ----------------------------------------------------------------- weights
     def _names(self):
@@ -76,12 +77,30 @@ class PagedAttention(Mixer):
         ops.linear(x, self.w_qkv, qkv)
         self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
         attn = self.rt.buffer("attn", tokens, self.q_dim)
-        ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, ctx.block_table[cache.group],
-                            ctx.seq_of_token[:tokens], ctx.positions[:tokens], self.nq, self.nkv, self.hd,
-                            cache.page_size, self.scale, self.window)
+        self._attend(qkv, attn, ctx, cache, tokens)
         out = self.rt.buffer("mixer_out", tokens, self.hidden)
         ops.linear(attn, self.w_o, out)
         return out
+
+
+    def _attend(self, qkv, attn, ctx, cache, tokens):
+        table = ctx.block_table[cache.group]
+        geometry = (self.nq, self.nkv, self.hd, cache.page_size, self.scale, self.window)
+        if not self._fast:
+            # the exact kernel: the whole 32-bit path, and bfloat16 sizes the tensor-core kernels refuse
+            ops.paged_attention(qkv, self.qkv_dim, attn, cache.k_pages, cache.v_pages, table, ctx.seq_of_token[:tokens],
+                                ctx.positions[:tokens], *geometry)
+            return
+        split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
+        if split > 0:
+            ops.paged_attention_prefill(qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table,
+                                        ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.decode_tail_seq, *geometry)
+        if tokens > split:
+            n = tokens - split
+            scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.hd, ctx.context_bound))
+            ops.paged_attention_decode(qkv[split:tokens], self.qkv_dim, attn[split:tokens], cache.k_pages, cache.v_pages, table,
+                                       ctx.seq_of_token[split:tokens], ctx.positions[split:tokens], scratch, *geometry,
+                                       ctx.context_bound)
 
 
 register_part("mixer", "attention", PagedAttention)

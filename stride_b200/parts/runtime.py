@@ -36,6 +36,17 @@ class Runtime:
             self._buffers[key] = buf
         return buf[:rows]
 
+    def scratch(self, tag: str, numel: int, dtype: torch.dtype = torch.float32):
+        """A flat scratch buffer of at least ``numel`` elements; it only ever grows,
+        and growing happens outside graph capture (the warm-up run of a bucket
+        asks for the same size as the captured run)."""
+        key = ("scratch", tag, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(int(numel), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf
+
     def shared(self, key, make):
         """One object per key for all parts (e.g. a rotary table shared by all layers)."""
         if key not in self._shared:

@@ -320,3 +320,80 @@ def test_sample_rows_draws_from_the_softmax(ops):
     out1 = torch.empty(1, dtype=torch.int32, device="cuda")
     ops.sample_rows(dev(uniform_logits), out1, temperature=dev(torch.ones(1)), uniform=dev(torch.tensor([0.35])))
     assert out1.item() == 3
+
+
+# ----------------------------------------------------------- tensor-core attention (bfloat16)
+def _seq_arrays(seqs):
+    q_start, q_len, ctx_len, at = [], [], [], 0
+    for ctx, new in seqs:
+        q_start.append(at)
+        q_len.append(new)
+        ctx_len.append(ctx + new)
+        at += new
+    mk = lambda v: torch.tensor(v, dtype=torch.int32)
+    return mk(q_start), mk(q_len), mk(ctx_len)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [
+    (8, 2, 128, 16, None), (3, 1, 64, 8, None), (16, 1, 64, 16, None), (4, 4, 128, 32, None), (8, 2, 128, 16, 200),
+    (6, 2, 64, 16, 5),
+])
+def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
+    g = torch.Generator().manual_seed(20)
+    dtype = torch.bfloat16
+    # contexts around the split size of 128 keys, a first token, and long ones
+    seqs = [(0, 1), (126, 1), (127, 1), (128, 1), (255, 1), (256, 1), (700, 1), (1500, 1), (31, 1)]
+    q, k_pages, v_pages, table, seq_of, pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, window, spike=(None, 3))
+    q = torch.cat([q, torch.zeros(1, nq * hd, dtype=dtype)])
+    seq_of = torch.cat([seq_of, torch.tensor([-1], dtype=torch.int32)])
+    pos = torch.cat([pos, torch.zeros(1, dtype=torch.int32)])
+    for bound in (1501, 4096):
+        out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+        scratch = torch.full((ops.decode_scratch_floats(q.shape[0], nq, hd, bound),), float("nan"), device="cuda")
+        ops.paged_attention_decode(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), scratch,
+                                   nq, nkv, hd, page, hd ** -0.5, window or 0, bound)
+        close(out[:-1], want, dtype)
+        assert float(out[-1].abs().max()) == 0.0
+    assert ops.fast_attention_supported(dtype, nq, nkv, hd)
+    assert not ops.fast_attention_supported(dtype, 34, 2, 128) and not ops.fast_attention_supported(dtype, 4, 2, 48)
+    assert not ops.fast_attention_supported(torch.float32, 4, 2, 128)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [
+    (8, 2, 128, 16, None), (3, 1, 64, 8, None), (4, 4, 128, 32, None), (8, 2, 128, 16, 70), (6, 2, 64, 16, 5), (4, 1, 128, 16, 64),
+])
+def test_prefill_attention_over_portions(ops, nq, nkv, hd, page, window):
+    g = torch.Generator().manual_seed(21)
+    dtype = torch.bfloat16
+    # whole prompts (one longer than several tiles), portions that start inside a page or a tile, tiny portions, one token
+    seqs = [(0, 200), (0, 64), (0, 65), (100, 37), (64, 2), (333, 130), (5, 1), (0, 1), (128, 63)]
+    q, k_pages, v_pages, table, _seq_of, _pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, window, spike=(None, 2))
+    q_start, q_len, ctx_len = _seq_arrays(seqs)
+    out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+    ops.paged_attention_prefill(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, window or 0)
+    close(out, want, dtype)
+    # only the first requests: the rows of the others are left alone
+    first = 3
+    rows = int(q_start[first])
+    out2 = torch.full((rows, nq * hd), 5.0, dtype=dtype, device="cuda")
+    ops.paged_attention_prefill(dev(q[:rows]), nq * hd, out2, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                dev(ctx_len), first, nq, nkv, hd, page, hd ** -0.5, window or 0)
+    assert torch.equal(out2, out[:rows])
+
+
+def test_prefill_attention_masks_the_future_and_the_far_past(ops):
+    """Negative control in the manner of the reference's off-by-one mask: keys after a
+    query, or before its window, must not leak, even with huge values behind the mask."""
+    g = torch.Generator().manual_seed(22)
+    nq, nkv, hd, page, window = 4, 2, 64, 16, 20
+    seqs = [(40, 90)]
+    q, k_pages, v_pages, table, _s, _p, want = _paged_case(g, torch.bfloat16, seqs, nq, nkv, hd, page, window)
+    q_start, q_len, ctx_len = _seq_arrays(seqs)
+    out = torch.empty(q.shape[0], nq * hd, dtype=torch.bfloat16, device="cuda")
+    args = (dev(table), dev(q_start), dev(q_len), dev(ctx_len), 1, nq, nkv, hd, page, hd ** -0.5)
+    ops.paged_attention_prefill(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), *args, window)
+    close(out, want, torch.bfloat16)
+    no_window = torch.empty_like(out)
+    ops.paged_attention_prefill(dev(q), nq * hd, no_window, dev(k_pages), dev(v_pages), *args, 0)
+    assert float((no_window.float() - out.float()).abs().max()) > 0.05, "the window changed nothing"
