@@ -172,9 +172,9 @@ def run_ours(args) -> dict:
     cfg, full_layers = bench_config(args.layers)
     batch, context, prompt_len = args.batch, args.context, 2048
     page = 16
-    need_tokens = max(64 * (context + 64), batch * (context + 256)) + 4096
+    need_tokens = max(64 * (context + 64), batch * (context + 1024)) + 4096
     engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=page, num_blocks=need_tokens // page + 64,
-                    max_batch_tokens=2048, max_batch_seqs=64, max_model_len=context + 512, prefix_caching=False,
+                    max_batch_tokens=2048, max_batch_seqs=64, max_model_len=context + 1024, prefix_caching=False,
                     check_invariants=False)
     for pages in engine.device_cache.pages:      # synthetic cache contents: small random keys and values
         pages.normal_(0.0, 0.5)
@@ -224,7 +224,9 @@ def run_ours(args) -> dict:
     e2e = None
     if not args.no_e2e:
         prompts = [torch.randint(0, cfg.vocab_size, (context - 1,), generator=g).tolist() for _ in range(batch)]
-        params = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 8, ignore_eos=True)
+        # requests that finish their prompt early keep decoding while the others are still prefilled in portions
+        spare = batch * (-(-context // 2048)) + 16
+        params = SamplingParams(temperature=0.0, max_tokens=max(args.warmup, 3) + args.steps + spare, ignore_eos=True)
         ids = [engine.add_request(p, params) for p in prompts]
         while engine.scheduler.num_waiting or any(engine.scheduler.sequence(engine._seq_of_request[i]).state != engine._rt.SeqState.Decoding
                                                   for i in ids):
@@ -234,11 +236,18 @@ def run_ours(args) -> dict:
         h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        produced = 0
+        produced, step_ms = 0, []
         for _ in range(args.steps):
+            t_step = time.perf_counter()
             produced += sum(1 for _rid, tok, _why in engine.step() if tok is not None)
+            step_ms.append((time.perf_counter() - t_step) * 1e3)
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t0
+        if os.environ.get("STRIDE_BENCH_DEBUG"):
+            print("e2e step ms:", [round(x, 2) for x in step_ms], file=sys.stderr)
+            print("metrics:", engine.metrics(), file=sys.stderr)
+        if produced != batch * args.steps:
+            raise RuntimeError(f"the end-to-end loop produced {produced} tokens, expected {batch * args.steps}")
         e2e = {"value": round(produced / elapsed, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // args.steps,
                "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // args.steps}

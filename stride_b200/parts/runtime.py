@@ -21,6 +21,7 @@ class Runtime:
         self.row_capacity = int(row_capacity)
         self._buffers: dict[tuple, torch.Tensor] = {}
         self._shared: dict = {}
+        self._retired: list = []
 
     def buffer(self, tag: str, rows: int, cols: int, dtype: torch.dtype | None = None, row_kind: str = "tokens"):
         """A [rows, cols] view of the buffer ``tag``. ``row_kind`` picks the
@@ -37,12 +38,15 @@ class Runtime:
         return buf[:rows]
 
     def scratch(self, tag: str, numel: int, dtype: torch.dtype = torch.float32):
-        """A flat scratch buffer of at least ``numel`` elements; it only ever grows,
+        """A flat scratch buffer of at least ``numel`` elements. It only ever grows,
         and growing happens outside graph capture (the warm-up run of a bucket
-        asks for the same size as the captured run)."""
+        asks for the same size as the captured run); a buffer that was outgrown
+        stays allocated, because an earlier graph may hold its address."""
         key = ("scratch", tag, dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self._retired.append(buf)      # a captured graph may still write to it: never hand it back
             buf = torch.empty(int(numel), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf

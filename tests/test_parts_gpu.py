@@ -140,7 +140,7 @@ def test_attention_mixer_alone_in_portions(gpu, name, dtype, tol, window, bias):
         def cache_requests(self):
             return [(mixer.cache_request(), None)]
     model = OneMixerModel()
-    device_cache = DeviceCache(model, page, 12, 4, dtype, "cuda")
+    device_cache = DeviceCache(model, page, 16 if window is None else 9, 4, dtype, "cuda")
     for p in device_cache.pages:
         p.fill_(float("nan"))
     cache = CacheManager(page, device_cache.group_configs(), 4, False)
@@ -172,4 +172,4 @@ def test_attention_mixer_alone_in_portions(gpu, name, dtype, tol, window, bias):
     assert held == lengths
     if window:
         assert cache.table(1, 0).count(-1) >= 6, "the window never gave a page back"
-        assert cache.stats()["live"] <= 5
+        assert cache.stats()["live"] <= 6
