@@ -274,6 +274,36 @@ def run_ours(args) -> dict:
     }
 
 
+def run_profile(args) -> dict:
+    """A few eager steps (no CUDA graph) of one kind, small enough to sit under a
+    profiler: ``--profile decode`` (batch x context synthetic cache) or
+    ``--profile prefill`` (one 2,048-token prompt)."""
+    import torch
+
+    from stride_b200 import Engine
+
+    cfg, full_layers = bench_config(args.layers)
+    batch, context = args.batch, args.context
+    engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=16,
+                    num_blocks=(batch * (context + 64) + 4096) // 16, max_batch_tokens=2048, max_batch_seqs=64,
+                    max_model_len=context + 512, prefix_caching=False, cuda_graphs=False)
+    for pages in engine.device_cache.pages:
+        pages.normal_(0.0, 0.5)
+    if args.profile == "decode":
+        step_batch, _ = _synthetic_decode_batch(engine, batch, context, 1000)
+    else:
+        g = torch.Generator().manual_seed(1)
+        engine.cache.open(1, "bench")
+        engine.cache.ensure(1, 2048, 0)
+        step_batch = engine._rt.StepBatch(engine.cache)
+        step_batch.add(1, torch.randint(0, cfg.vocab_size, (2048,), generator=g).tolist(), 0, [2047])
+    for _ in range(args.warmup + args.steps):
+        engine.runner.step(step_batch)
+    torch.cuda.synchronize()
+    return {"profiled": args.profile, "layers": cfg.num_hidden_layers, "layers_of_named_config": full_layers, "batch": batch,
+            "context": context, "steps": args.warmup + args.steps}
+
+
 # --------------------------------------------------------------------- reference
 def run_reference(args) -> dict:
     ref = os.path.join(ROOT, "baseline", "_ref")
@@ -364,11 +394,16 @@ def main(argv=None) -> int:
     p.add_argument("--context", type=int, default=8192)
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (reported in config)")
     p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    p.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                   help="run a few eager steps of one kind for a profiler instead of measuring")
     args = p.parse_args(argv)
     if args.gpus != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"unsupported": f"this engine runs on one GPU; --gpus {args.gpus} is not measured"}))
         return 2
+    if args.profile:
+        print(json.dumps(run_profile(args)))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
