@@ -53,15 +53,20 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
     unsigned char* vs = smem + kSplitKeys * ROW_BYTES + warp * kWarpKeys * ROW_BYTES;
 
     if (warp_valid) {
+        // Lane r looks up where key wlo + r lives (one division per lane, not per 16-byte chunk).
+        int my_row = -1;
+        {
+            const int key = wlo + lane;
+            if (key >= first && key <= pos) my_row = (table[key / page_size] * nkv + kvh) * page_size + key % page_size;
+        }
 #pragma unroll
         for (int i = 0; i < kWarpKeys * CHUNKS / 32; ++i) {
             const int idx = i * 32 + lane;
             const int row = idx / CHUNKS, c = idx % CHUNKS;
-            const int key = wlo + row;
+            const int src_row = __shfl_sync(0xffffffffu, my_row, row);
             const uint32_t off = swizzled<ROW_BYTES>(row, c);
-            if (key >= first && key <= pos) {
-                const int page = table[key / page_size];
-                const size_t src = ((static_cast<size_t>(page) * nkv + kvh) * page_size + key % page_size) * HD + c * 8;
+            if (src_row >= 0) {
+                const size_t src = static_cast<size_t>(src_row) * HD + c * 8;
                 cp_async_16(ks + off, k_pages + src);
                 cp_async_16(vs + off, v_pages + src);
             } else {   // masked keys: zeros, so that 0 * value stays 0
@@ -226,14 +231,27 @@ paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restr
     const int s_lo = first / kSplitKeys, s_hi = pos / kSplitKeys;
     const size_t base = (static_cast<size_t>(t) * nq + head) * num_splits;
     float mm = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-    float acc = 0.f, sum = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-        const float f = exp2f(part_ml[(base + s) * 2] - mm);
-        acc += f * part_o[(base + s) * HD + d];
-        sum += f * part_ml[(base + s) * 2 + 1];
+    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, __ldg(part_ml + (base + s) * 2));
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, sum = 0.f;
+    int s = s_lo;
+    for (; s + 3 <= s_hi; s += 4) {      // four independent loads in flight
+        float f[4], v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f[j] = exp2f(__ldg(part_ml + (base + s + j) * 2) - mm);
+            v[j] = __ldg(part_o + (base + s + j) * HD + d);
+            sum += f[j] * __ldg(part_ml + (base + s + j) * 2 + 1);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] += f[j] * v[j];
     }
-    dst[d] = __float2bfloat16_rn(acc / sum);
+    for (; s <= s_hi; ++s) {
+        const float f = exp2f(__ldg(part_ml + (base + s) * 2) - mm);
+        acc[0] += f * __ldg(part_o + (base + s) * HD + d);
+        sum += f * __ldg(part_ml + (base + s) * 2 + 1);
+    }
+    const float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    dst[d] = __float2bfloat16_rn(total / sum);
 }
 
 template <int HD>

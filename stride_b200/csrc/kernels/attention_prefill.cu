@@ -139,16 +139,29 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
             }
         }
         float mx[2] = {-INFINITY, -INFINITY};
+        // Only tiles that touch the diagonal or the window's edge need the mask.
+        const int warp_first_pos = pos0 + min(wr0, rows - 1);
+        const bool needs_mask = k0 + kKTile - 1 > warp_first_pos || (window > 0 && k0 <= warp_last_pos - window);
+        if (needs_mask) {
 #pragma unroll
-        for (int nt = 0; nt < kKTile / 8; ++nt)
+            for (int nt = 0; nt < kKTile / 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = k0 + nt * 8 + 2 * tg + (e & 1);
-                const int p = (e >> 1) ? pos_b : pos_a;
-                const bool ok = key <= p && (window <= 0 || key > p - window);
-                s[nt][e] = ok ? s[nt][e] * scale_log2e : -INFINITY;
-                mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    const int key = k0 + nt * 8 + 2 * tg + (e & 1);
+                    const int p = (e >> 1) ? pos_b : pos_a;
+                    const bool ok = key <= p && (window <= 0 || key > p - window);
+                    s[nt][e] = ok ? s[nt][e] * scale_log2e : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < kKTile / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    s[nt][e] *= scale_log2e;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+        }
         float corr[2], base[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {

@@ -5,6 +5,8 @@
 // Reductions, rotation angles and the residual sum are float32 in every mode.
 // The residual stream itself is float32 in both modes; activations between the
 // matrix products have the model's element type T (float or bfloat16).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace stride {
@@ -135,6 +137,203 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
     out[idx] = from_f32<T>(silu * u);
 }
 
+// ------------------------------------------------------------------ 16-byte vectors
+// A pack of V consecutive elements that is loaded and stored with one 16-byte
+// access (4 floats or 8 bfloat16).
+template <typename T>
+struct Pack;
+template <>
+struct Pack<float> {
+    static constexpr int V = 4;
+    float v[4];
+    __device__ __forceinline__ void load(const float* p) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct Pack<__nv_bfloat16> {
+    static constexpr int V = 8;
+    float v[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = raw;
+    }
+};
+
+// Same arithmetic as add_rmsnorm_kernel, four columns per thread and the row
+// kept in registers (hidden <= 4 * ITERS * blockDim.x, hidden % 4 == 0).
+template <typename T, int ITERS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int32_t* __restrict__ rows, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const size_t s = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+    float* res = residual + s * hidden;
+    const T* del = delta ? delta + s * hidden : nullptr;
+    float4 x[ITERS];
+    float sq = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        if (c < hidden) {
+            x[it] = *reinterpret_cast<const float4*>(res + c);
+            if (del) {
+                float d[4];
+                if constexpr (sizeof(T) == 2) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(del + c);
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+                    d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
+                } else {
+                    const float4 t = *reinterpret_cast<const float4*>(del + c);
+                    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+                }
+                x[it].x = __fadd_rn(x[it].x, d[0]);
+                x[it].y = __fadd_rn(x[it].y, d[1]);
+                x[it].z = __fadd_rn(x[it].z, d[2]);
+                x[it].w = __fadd_rn(x[it].w, d[3]);
+                if (!rows) *reinterpret_cast<float4*>(res + c) = x[it];
+            }
+            sq = fmaf(x[it].x, x[it].x, sq);
+            sq = fmaf(x[it].y, x[it].y, sq);
+            sq = fmaf(x[it].z, x[it].z, sq);
+            sq = fmaf(x[it].w, x[it].w, sq);
+        }
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    T* dst = out + static_cast<size_t>(r) * hidden;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        if (c < hidden) {
+            const float4 w = *reinterpret_cast<const float4*>(weight + c);
+            const float y0 = __fmul_rn(__fmul_rn(x[it].x, inv), w.x), y1 = __fmul_rn(__fmul_rn(x[it].y, inv), w.y);
+            const float y2 = __fmul_rn(__fmul_rn(x[it].z, inv), w.z), y3 = __fmul_rn(__fmul_rn(x[it].w, inv), w.w);
+            if constexpr (sizeof(T) == 2) {
+                uint2 raw;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+                h[0] = __floats2bfloat162_rn(y0, y1);
+                h[1] = __floats2bfloat162_rn(y2, y3);
+                *reinterpret_cast<uint2*>(dst + c) = raw;
+            } else {
+                *reinterpret_cast<float4*>(dst + c) = make_float4(y0, y1, y2, y3);
+            }
+        }
+    }
+}
+
+// rope_kv_write_kernel with 16-byte accesses: one unit of work is V consecutive
+// pair indices of one head (needs hd / 2 to be a multiple of V).
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                                         const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
+                                         const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                         T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd,
+                                         int page_size, int rotate) {
+    constexpr int V = Pack<T>::V;
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int per_head = half / V;
+    const int heads = nq + 2 * nkv;
+    const int pos = positions[t];
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    T* row = qkv + static_cast<size_t>(t) * heads * hd;
+    const float* cs = cos_table + static_cast<size_t>(pos) * half;
+    const float* sn = sin_table + static_cast<size_t>(pos) * half;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int offset = slot >= 0 ? slot % page_size : 0;
+    for (int w = threadIdx.x; w < heads * per_head; w += blockDim.x) {
+        const int head = w / per_head, i = (w - head * per_head) * V;
+        T* x = row + head * hd;
+        Pack<T> a, b;
+        a.load(x + i);
+        b.load(x + i + half);
+        if (bias) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                a.v[j] = __fadd_rn(a.v[j], bias[head * hd + i + j]);
+                b.v[j] = __fadd_rn(b.v[j], bias[head * hd + i + half + j]);
+            }
+        }
+        if (head < nq + nkv && rotate) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const float c = cs[i + j], s = sn[i + j];
+                const float ra = __fadd_rn(__fmul_rn(a.v[j], c), __fmul_rn(-b.v[j], s));
+                const float rb = __fadd_rn(__fmul_rn(b.v[j], c), __fmul_rn(a.v[j], s));
+                a.v[j] = ra;
+                b.v[j] = rb;
+            }
+        }
+        if (head < nq) {
+            a.store(x + i);
+            b.store(x + i + half);
+        } else if (slot >= 0) {
+            const bool is_key = head < nq + nkv;
+            const int kvh = is_key ? head - nq : head - nq - nkv;
+            T* dst = (is_key ? k_pages : v_pages) + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * hd;
+            a.store(dst + i);
+            b.store(dst + i + half);
+        }
+    }
+}
+
+// silu_mul_kernel with 16-byte accesses (inter % V == 0).
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t packs) {
+    constexpr int V = Pack<T>::V;
+    const int per_row = inter / V;
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < packs;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = idx / per_row;
+        const int i = static_cast<int>(idx - t * per_row) * V;
+        Pack<T> g, u;
+        g.load(in + t * 2 * inter + i);
+        u.load(in + t * 2 * inter + inter + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) g.v[j] = (g.v[j] / (1.f + expf(-g.v[j]))) * u.v[j];
+        g.store(out + t * inter + i);
+    }
+}
+
+// embed_gather_kernel with 16-byte reads of the table (hidden % V == 0).
+template <typename T>
+__global__ void embed_gather_vec_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ seq_of_token,
+                                        const T* __restrict__ table, float* __restrict__ out, int hidden, int vocab) {
+    constexpr int V = Pack<T>::V;
+    const int t = blockIdx.x;
+    const bool live = seq_of_token == nullptr || seq_of_token[t] >= 0;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const T* row = table + static_cast<size_t>(id) * hidden;
+    float* dst = out + static_cast<size_t>(t) * hidden;
+    for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
+        Pack<T> p;
+        if (live) p.load(row + i);
+#pragma unroll
+        for (int j = 0; j < V; j += 4)
+            *reinterpret_cast<float4*>(dst + i + j) =
+                live ? make_float4(p.v[j], p.v[j + 1], p.v[j + 2], p.v[j + 3]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -146,12 +345,20 @@ int stride_embed_gather(const int32_t* ids, const int32_t* seq_of_token, const v
     if (tokens < 0 || hidden <= 0 || vocab <= 0) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
-    if (dtype == STRIDE_DTYPE_F32)
-        embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
-    else if (dtype == STRIDE_DTYPE_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
-    else
+    const bool aligned = (reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+    if (dtype == STRIDE_DTYPE_F32) {
+        if (aligned && hidden % 4 == 0)
+            embed_gather_vec_kernel<float><<<tokens, 128, 0, stream>>>(ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
+        else
+            embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
+    } else if (dtype == STRIDE_DTYPE_BF16) {
+        if (aligned && hidden % 8 == 0)
+            embed_gather_vec_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
+        else
+            embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
+    } else {
         return STRIDE_BAD_ARGUMENT;
+    }
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -159,6 +366,31 @@ int stride_add_rmsnorm(float* residual, const void* delta, const float* weight, 
                        int num_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
     if (num_rows < 0 || hidden <= 0) return STRIDE_BAD_ARGUMENT;
     if (num_rows == 0) return 0;
+    {
+        // Vector path: the row stays in registers, four columns per thread.
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
+                               reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out);
+        const int quads = hidden / 4;
+        if (hidden % 4 == 0 && bits % 16 == 0 && quads <= 8 * 256 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
+            const int threads = quads <= 32 ? 32 : (quads <= 64 ? 64 : (quads <= 128 ? 128 : 256));
+            const int iters = (quads + threads - 1) / threads;
+#define STRIDE_NORM_LAUNCH(T, I)                                                                                            \
+    add_rmsnorm_vec_kernel<T, I><<<num_rows, threads, 0, stream>>>(residual, static_cast<const T*>(delta), weight,         \
+                                                                   static_cast<T*>(out), rows, hidden, eps)
+#define STRIDE_NORM_DISPATCH(T)                                                                                             \
+    do {                                                                                                                   \
+        if (iters <= 1) STRIDE_NORM_LAUNCH(T, 1);                                                                          \
+        else if (iters <= 2) STRIDE_NORM_LAUNCH(T, 2);                                                                     \
+        else if (iters <= 4) STRIDE_NORM_LAUNCH(T, 4);                                                                     \
+        else STRIDE_NORM_LAUNCH(T, 8);                                                                                     \
+    } while (0)
+            if (dtype == STRIDE_DTYPE_F32) STRIDE_NORM_DISPATCH(float);
+            else STRIDE_NORM_DISPATCH(__nv_bfloat16);
+#undef STRIDE_NORM_DISPATCH
+#undef STRIDE_NORM_LAUNCH
+            return STRIDE_LAUNCH_STATUS();
+        }
+    }
     const size_t smem = (static_cast<size_t>(hidden) + 32) * sizeof(float);
     if (smem > 200 * 1024) return STRIDE_UNSUPPORTED;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -195,6 +427,19 @@ int stride_rope_kv_write(void* qkv, const float* bias, const int32_t* positions,
     if (tokens == 0) return 0;
     const int work = (nq + 2 * nkv) * (hd / 2);
     const int threads = work >= 1024 ? 256 : 128;
+    {
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages);
+        const int vec = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
+        if (bits % 16 == 0 && (hd / 2) % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
+            const int units = work / vec;
+            const int vthreads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
+            if (dtype == STRIDE_DTYPE_F32)
+                rope_kv_write_vec_kernel<float><<<tokens, vthreads, 0, stream>>>(static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
+            else
+                rope_kv_write_vec_kernel<__nv_bfloat16><<<tokens, vthreads, 0, stream>>>(static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
+            return STRIDE_LAUNCH_STATUS();
+        }
+    }
     if (dtype == STRIDE_DTYPE_F32)
         rope_kv_write_kernel<float><<<tokens, threads, 0, stream>>>(static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
     else if (dtype == STRIDE_DTYPE_BF16)
@@ -209,6 +454,19 @@ int stride_silu_mul(const void* in, void* out, int tokens, int inter, int dtype,
     if (tokens == 0) return 0;
     const size_t total = static_cast<size_t>(tokens) * inter;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+    {
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
+        const int vec = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
+        if (bits % 16 == 0 && inter % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
+            const size_t packs = total / vec;
+            const unsigned vblocks = static_cast<unsigned>(std::min<size_t>((packs + 255) / 256, 148 * 16));
+            if (dtype == STRIDE_DTYPE_F32)
+                silu_mul_vec_kernel<float><<<vblocks, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), inter, packs);
+            else
+                silu_mul_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, packs);
+            return STRIDE_LAUNCH_STATUS();
+        }
+    }
     if (dtype == STRIDE_DTYPE_F32)
         silu_mul_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), inter, total);
     else if (dtype == STRIDE_DTYPE_BF16)
