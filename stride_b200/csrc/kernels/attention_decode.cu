@@ -2,14 +2,15 @@
 //
 // A decoded token reads every key of its request, so the step is bound by the
 // memory bandwidth; with few requests there are too few (request, head) pairs to
-// fill 148 SMs. The keys are therefore cut into splits of 128: one CTA handles
+// fill 148 SMs. The keys are therefore cut into splits (a multiple of 64 keys,
+// chosen from the launch's sizes): one CTA handles
 // (split, key head, token), multiplies the whole query group of that key head
 // (nq / nkv heads, padded to the 16 rows of an m16n8k16 tile) with its keys on
 // the tensor cores, keeps an online softmax in float32, and writes an
 // unnormalised partial result. A second kernel merges the splits of each
-// (token, query head). All loads of a CTA are issued at once with cp.async, each
-// warp fetching exactly the 32 keys and values it works on, so several CTAs per
-// SM keep enough bytes in flight without a staged pipeline.
+// (token, query head). Each warp walks its own 16-key tiles through a private
+// two-stage cp.async ring (no block-wide barrier inside the loop), so every
+// resident CTA always has copies in flight while it computes.
 //
 // The rule is that of python/stride_worker/layers.py:109-149 for a single query
 // at position p: keys j <= p (and j > p - window), softmax(q k^T * scale) v, query
@@ -20,8 +21,9 @@
 
 namespace stride {
 
-constexpr int kSplitKeys = 128;   // keys per CTA
-constexpr int kWarpKeys = 32;     // keys per warp
+constexpr int kTileKeys = 16;     // keys one warp works on at a time
+constexpr int kGroupKeys = 64;    // keys the four warps of a CTA cover per pipeline stage
+constexpr int kStages = 2;
 
 template <int HD>
 __global__ void __launch_bounds__(128)
@@ -29,10 +31,11 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
                           const __nv_bfloat16* __restrict__ v_pages, const int32_t* __restrict__ block_table,
                           int table_width, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions,
                           float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int page_size,
-                          float scale_log2e, int window, int num_splits) {
+                          float scale_log2e, int window, int split_keys, int num_splits) {
     constexpr int ROW_BYTES = HD * 2;
     constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
+    constexpr int TILE_BYTES = kTileKeys * ROW_BYTES;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -40,42 +43,51 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
     if (seq < 0) return;
     const int pos = positions[t];
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int lo = split * kSplitKeys;
-    if (lo > pos || lo + kSplitKeys <= first) return;   // uniform for the CTA
+    const int lo = split * split_keys;
+    if (lo > pos || lo + split_keys <= first) return;   // uniform for the CTA
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tg = lane & 3;
     const int group = nq / nkv;
-    const int wlo = lo + warp * kWarpKeys;
-    const bool warp_valid = !(wlo > pos || wlo + kWarpKeys <= first);
     const int32_t* table = block_table + static_cast<size_t>(seq) * table_width;
-    unsigned char* ks = smem + warp * kWarpKeys * ROW_BYTES;
-    unsigned char* vs = smem + kSplitKeys * ROW_BYTES + warp * kWarpKeys * ROW_BYTES;
+    const int n_tiles = split_keys / kGroupKeys;          // tiles this warp walks: tile j holds keys base(j) .. +15
+    auto tile_base = [&](int j) { return lo + j * kGroupKeys + warp * kTileKeys; };
+    auto tile_live = [&](int j) { const int b = tile_base(j); return j < n_tiles && b <= pos && b + kTileKeys > first; };
+    // Each warp owns a ring of kStages (keys, values) tiles; no other warp touches it.
+    auto k_stage = [&](int stage) { return smem + (stage * 4 + warp) * 2 * TILE_BYTES; };
 
-    if (warp_valid) {
-        // Lane r looks up where key wlo + r lives (one division per lane, not per 16-byte chunk).
-        int my_row = -1;
-        {
-            const int key = wlo + lane;
-            if (key >= first && key <= pos) my_row = (table[key / page_size] * nkv + kvh) * page_size + key % page_size;
-        }
+    // Starts the copies of tile j into its stage. Always commits one group, so that
+    // "all but the newest group have landed" means the same thing in every iteration.
+    auto issue = [&](int j) {
+        if (tile_live(j)) {
+            unsigned char* ks = k_stage(j % kStages);
+            unsigned char* vs = ks + TILE_BYTES;
+            int my_row = -1;   // lane r < 16 looks up where key base + r lives: one division per key, not per chunk
+            {
+                const int key = tile_base(j) + lane;
+                if (lane < kTileKeys && key >= first && key <= pos)
+                    my_row = (table[key / page_size] * nkv + kvh) * page_size + key % page_size;
+            }
 #pragma unroll
-        for (int i = 0; i < kWarpKeys * CHUNKS / 32; ++i) {
-            const int idx = i * 32 + lane;
-            const int row = idx / CHUNKS, c = idx % CHUNKS;
-            const int src_row = __shfl_sync(0xffffffffu, my_row, row);
-            const uint32_t off = swizzled<ROW_BYTES>(row, c);
-            if (src_row >= 0) {
-                const size_t src = static_cast<size_t>(src_row) * HD + c * 8;
-                cp_async_16(ks + off, k_pages + src);
-                cp_async_16(vs + off, v_pages + src);
-            } else {   // masked keys: zeros, so that 0 * value stays 0
-                *reinterpret_cast<uint4*>(ks + off) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < kTileKeys * CHUNKS / 32; ++i) {
+                const int idx = i * 32 + lane;
+                const int row = idx / CHUNKS, c = idx % CHUNKS;
+                const int src_row = __shfl_sync(0xffffffffu, my_row, row);
+                const uint32_t off = swizzled<ROW_BYTES>(row, c);
+                if (src_row >= 0) {
+                    const size_t src = static_cast<size_t>(src_row) * HD + c * 8;
+                    cp_async_16(ks + off, k_pages + src);
+                    cp_async_16(vs + off, v_pages + src);
+                } else {   // masked keys: zeros, so that 0 * value stays 0
+                    *reinterpret_cast<uint4*>(ks + off) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+                }
             }
         }
         cp_async_commit();
-    }
+    };
+    issue(0);
+    issue(1);
 
     // The query group as the A operand: row r is query head kvh * group + r.
     uint32_t qa[KSTEPS][4];
@@ -97,20 +109,18 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-    if (warp_valid) {
-        cp_async_wait<0>();
+    const int lm = lane >> 3, lr = lane & 7;     // ldmatrix: matrix index and row within it
+    for (int j = 0; j < n_tiles; ++j) {
+        cp_async_wait<kStages - 1>();              // tile j has landed (only the newest group may be pending)
         __syncwarp();
-        const uint32_t ks_addr = smem_addr(ks), vs_addr = smem_addr(vs);
-        const int lm = lane >> 3, lr = lane & 7;     // ldmatrix: matrix index and row within it
-#pragma unroll
-        for (int tile = 0; tile < kWarpKeys / 16; ++tile) {
-            const int tlo = wlo + tile * 16;
-            if (tlo > pos || tlo + 16 <= first) continue;
+        if (tile_live(j)) {
+            const int tlo = tile_base(j);
+            const uint32_t ks_addr = smem_addr(k_stage(j % kStages)), vs_addr = ks_addr + TILE_BYTES;
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
                 uint32_t b[4];
-                ldmatrix_x4(b, ks_addr + swizzled<ROW_BYTES>(tile * 16 + (lm >> 1) * 8 + lr, kk * 2 + (lm & 1)));
+                ldmatrix_x4(b, ks_addr + swizzled<ROW_BYTES>((lm >> 1) * 8 + lr, kk * 2 + (lm & 1)));
                 mma_bf16_16816(s[0], qa[kk], b[0], b[1]);
                 mma_bf16_16816(s[1], qa[kk], b[2], b[3]);
             }
@@ -159,11 +169,13 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
 #pragma unroll
             for (int dn = 0; dn < HD / 16; ++dn) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, vs_addr + swizzled<ROW_BYTES>(tile * 16 + (lm & 1) * 8 + lr, dn * 2 + (lm >> 1)));
+                ldmatrix_x4_trans(b, vs_addr + swizzled<ROW_BYTES>((lm & 1) * 8 + lr, dn * 2 + (lm >> 1)));
                 mma_bf16_16816(o[2 * dn], pa, b[0], b[1]);
                 mma_bf16_16816(o[2 * dn + 1], pa, b[2], b[3]);
             }
         }
+        __syncwarp();                              // every lane is done with the stage before it is refilled
+        issue(j + kStages);
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -215,11 +227,16 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
 }
 
 // out[t, head, :] = sum_s w_s * part_o[s] / sum_s w_s * part_l[s], w_s = 2^(m_s - max m).
+// One block per (head, token): the weights of the splits are computed once, in
+// parallel over the splits, then every thread sums its column with the loads of
+// several splits in flight.
 template <int HD>
 __global__ void __launch_bounds__(HD)
 paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                           __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
-                          const int32_t* __restrict__ positions, int nq, int window, int num_splits) {
+                          const int32_t* __restrict__ positions, int nq, int window, int split_keys, int num_splits) {
+    extern __shared__ float weights[];          // num_splits floats, then 32 for the reductions
+    float* scratch = weights + num_splits;
     const int head = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     __nv_bfloat16* dst = out + (static_cast<size_t>(t) * nq + head) * HD;
     if (seq_of_token[t] < 0) {
@@ -228,38 +245,49 @@ paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restr
     }
     const int pos = positions[t];
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = first / kSplitKeys, s_hi = pos / kSplitKeys;
-    const size_t base = (static_cast<size_t>(t) * nq + head) * num_splits;
-    float mm = -INFINITY;
-    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, __ldg(part_ml + (base + s) * 2));
-    float acc[4] = {0.f, 0.f, 0.f, 0.f}, sum = 0.f;
-    int s = s_lo;
-    for (; s + 3 <= s_hi; s += 4) {      // four independent loads in flight
-        float f[4], v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            f[j] = exp2f(__ldg(part_ml + (base + s + j) * 2) - mm);
-            v[j] = __ldg(part_o + (base + s + j) * HD + d);
-            sum += f[j] * __ldg(part_ml + (base + s + j) * 2 + 1);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] += f[j] * v[j];
+    const int s_lo = first / split_keys, n = pos / split_keys - s_lo + 1;
+    const size_t base = (static_cast<size_t>(t) * nq + head) * num_splits + s_lo;
+    float mine = -INFINITY;
+    for (int s = d; s < n; s += HD) mine = fmaxf(mine, part_ml[(base + s) * 2]);
+    const float mm = block_max(mine, scratch);
+    float lsum = 0.f;
+    for (int s = d; s < n; s += HD) {
+        const float w = exp2f(part_ml[(base + s) * 2] - mm);
+        weights[s] = w;
+        lsum += w * part_ml[(base + s) * 2 + 1];
     }
-    for (; s <= s_hi; ++s) {
-        const float f = exp2f(__ldg(part_ml + (base + s) * 2) - mm);
-        acc[0] += f * __ldg(part_o + (base + s) * HD + d);
-        sum += f * __ldg(part_ml + (base + s) * 2 + 1);
+    const float total_l = block_sum(lsum, scratch);     // its barriers also publish `weights`
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* col = part_o + base * HD + d;
+    int s = 0;
+    for (; s + 3 < n; s += 4) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = col[static_cast<size_t>(s + j) * HD];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(weights[s + j], v[j], acc[j]);
     }
-    const float total = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    dst[d] = __float2bfloat16_rn(total / sum);
+    for (; s < n; ++s) acc[0] = fmaf(weights[s], col[static_cast<size_t>(s) * HD], acc[0]);
+    dst[d] = __float2bfloat16_rn(((acc[0] + acc[1]) + (acc[2] + acc[3])) / total_l);
+}
+
+// Keys per CTA: a multiple of 64, grown until the grid is about eight waves of
+// resident CTAs, so that few requests still fill the SMs and many requests do not
+// drown in partial results. It depends only on the launch's sizes (not on the
+// contexts of the moment), so a captured graph stays valid.
+inline int choose_split_keys(int tokens, int nkv, int max_context) {
+    const long long groups = static_cast<long long>(tokens) * nkv * ((max_context + kGroupKeys - 1) / kGroupKeys);
+    long long u = groups / (148LL * 3 * 8);
+    u = u < 1 ? 1 : (u > 16 ? 16 : u);
+    return static_cast<int>(u) * kGroupKeys;
 }
 
 template <int HD>
 int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
                   const __nv_bfloat16* v_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                   const int32_t* positions, float* part_o, float* part_ml, int tokens, int nq, int nkv, int page_size,
-                  float scale, int window, int num_splits, cudaStream_t stream) {
-    const int smem = 2 * kSplitKeys * HD * 2;
+                  float scale, int window, int split_keys, int num_splits, cudaStream_t stream) {
+    const int smem = kStages * 4 * 2 * kTileKeys * HD * 2;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -269,9 +297,10 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
     dim3 grid(num_splits, nkv, tokens);
     paged_decode_split_kernel<HD><<<grid, 128, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width,
                                                                seq_of_token, positions, part_o, part_ml, nq, nkv, page_size,
-                                                               scale * 1.4426950408889634f, window, num_splits);
-    paged_decode_merge_kernel<HD><<<dim3(nq, tokens), HD, 0, stream>>>(part_o, part_ml, out, seq_of_token, positions, nq,
-                                                                       window, num_splits);
+                                                               scale * 1.4426950408889634f, window, split_keys, num_splits);
+    const int merge_smem = (num_splits + 32) * static_cast<int>(sizeof(float));
+    paged_decode_merge_kernel<HD><<<dim3(nq, tokens), HD, merge_smem, stream>>>(part_o, part_ml, out, seq_of_token, positions,
+                                                                                nq, window, split_keys, num_splits);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -282,8 +311,10 @@ using namespace stride;
 extern "C" {
 
 // Number of float32 scratch elements the launcher needs for these sizes.
-long long stride_paged_decode_scratch_floats(int tokens, int nq, int hd, int max_context) {
-    const long long splits = (max_context + kSplitKeys - 1) / kSplitKeys;
+long long stride_paged_decode_scratch_floats(int tokens, int nq, int nkv, int hd, int max_context) {
+    if (tokens <= 0 || nq <= 0 || nkv <= 0 || max_context <= 0) return 0;
+    const int split_keys = choose_split_keys(tokens, nkv, max_context);
+    const long long splits = (max_context + split_keys - 1) / split_keys;
     return static_cast<long long>(tokens) * nq * splits * (hd + 2);
 }
 
@@ -300,8 +331,10 @@ int stride_paged_decode_attention(const void* q, int q_stride, void* out, const 
     if (nq % nkv) return STRIDE_BAD_ARGUMENT;
     if ((hd != 64 && hd != 128) || nq / nkv > 16 || tokens > 65535 || nkv > 65535 || q_stride % 2) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
-    const int num_splits = (max_context + kSplitKeys - 1) / kSplitKeys;
-    const long long need = stride_paged_decode_scratch_floats(tokens, nq, hd, max_context);
+    const int split_keys = choose_split_keys(tokens, nkv, max_context);
+    const int num_splits = (max_context + split_keys - 1) / split_keys;
+    if (num_splits > 8192) return STRIDE_UNSUPPORTED;
+    const long long need = stride_paged_decode_scratch_floats(tokens, nq, nkv, hd, max_context);
     if (scratch == nullptr || scratch_floats < need) return STRIDE_BAD_ARGUMENT;
     float* part_o = scratch;
     float* part_ml = scratch + static_cast<long long>(tokens) * nq * num_splits * hd;
@@ -311,9 +344,9 @@ int stride_paged_decode_attention(const void* q, int q_stride, void* out, const 
     auto vp = static_cast<const __nv_bfloat16*>(v_pages);
     if (hd == 64)
         return launch_decode<64>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
-                                 tokens, nq, nkv, page_size, scale, window, num_splits, stream);
+                                 tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
     return launch_decode<128>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
-                              tokens, nq, nkv, page_size, scale, window, num_splits, stream);
+                              tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
 }
 
 }  // extern "C"

@@ -192,16 +192,20 @@ def paged_attention(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of
         _code(q.dtype), _stream()), "paged_attention")
 
 
-DECODE_SPLIT_KEYS = 128
-
-
 def fast_attention_supported(dtype, nq: int, nkv: int, hd: int) -> bool:
     """Sizes that the tensor-core attention kernels run; others use the generic kernel."""
     return dtype == torch.bfloat16 and hd in (64, 128) and nq % nkv == 0 and nq // nkv <= 16
 
 
-def decode_scratch_floats(tokens: int, nq: int, hd: int, max_context: int) -> int:
-    return tokens * nq * (-(-max_context // DECODE_SPLIT_KEYS)) * (hd + 2)
+def decode_scratch_floats(tokens: int, nq: int, nkv: int, hd: int, max_context: int) -> int:
+    """float32 elements of scratch that ``paged_attention_decode`` needs for these sizes."""
+    f = _bound.get("stride_paged_decode_scratch_floats")
+    if f is None:
+        f = build.load_kernel_library("attention_decode").stride_paged_decode_scratch_floats
+        f.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        f.restype = c_longlong
+        _bound["stride_paged_decode_scratch_floats"] = f
+    return int(f(tokens, nq, nkv, hd, max_context))
 
 
 def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,

@@ -97,7 +97,7 @@ class PagedAttention(Mixer):
                                         ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.decode_tail_seq, *geometry)
         if tokens > split:
             n = tokens - split
-            scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.hd, ctx.context_bound))
+            scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.nkv, self.hd, ctx.context_bound))
             ops.paged_attention_decode(qkv[split:tokens], self.qkv_dim, attn[split:tokens], cache.k_pages, cache.v_pages, table,
                                        ctx.seq_of_token[split:tokens], ctx.positions[split:tokens], scratch, *geometry,
                                        ctx.context_bound)

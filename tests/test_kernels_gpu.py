@@ -347,9 +347,9 @@ def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
     q = torch.cat([q, torch.zeros(1, nq * hd, dtype=dtype)])
     seq_of = torch.cat([seq_of, torch.tensor([-1], dtype=torch.int32)])
     pos = torch.cat([pos, torch.zeros(1, dtype=torch.int32)])
-    for bound in (1501, 4096):
+    for bound in (1501, 4096, 200000):
         out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
-        scratch = torch.full((ops.decode_scratch_floats(q.shape[0], nq, hd, bound),), float("nan"), device="cuda")
+        scratch = torch.full((ops.decode_scratch_floats(q.shape[0], nq, nkv, hd, bound),), float("nan"), device="cuda")
         ops.paged_attention_decode(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), scratch,
                                    nq, nkv, hd, page, hd ** -0.5, window or 0, bound)
         close(out[:-1], want, dtype)
