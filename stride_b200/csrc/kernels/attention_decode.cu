@@ -16,6 +16,8 @@
 // at position p: keys j <= p (and j > p - window), softmax(q k^T * scale) v, query
 // head h reading key head h / (nq / nkv). Scratch: part_o[token][head][split][hd]
 // and part_ml[token][head][split][2] (running maximum in the log2 domain, sum).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -271,14 +273,21 @@ paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restr
     dst[d] = __float2bfloat16_rn(((acc[0] + acc[1]) + (acc[2] + acc[3])) / total_l);
 }
 
-// Keys per CTA: a multiple of 64, grown until the grid is about eight waves of
-// resident CTAs, so that few requests still fill the SMs and many requests do not
-// drown in partial results. It depends only on the launch's sizes (not on the
+// Keys per CTA: a multiple of 64 between 128 and 1024, chosen so that the grid is
+// two to three waves of resident CTAs (measured on a B200 at 8k context: every
+// CTA pays a fixed start-up of dependent loads, so fewer, longer CTAs win as long
+// as the SMs stay filled). It depends only on the launch's sizes (not on the
 // contexts of the moment), so a captured graph stays valid.
 inline int choose_split_keys(int tokens, int nkv, int max_context) {
+    static const int forced = [] {      // tuning hook: STRIDE_DECODE_SPLIT_KEYS=<multiple of 64>
+        const char* e = getenv("STRIDE_DECODE_SPLIT_KEYS");
+        const int v = e ? atoi(e) : 0;
+        return v > 0 ? (v + kGroupKeys - 1) / kGroupKeys * kGroupKeys : 0;
+    }();
+    if (forced) return forced;
     const long long groups = static_cast<long long>(tokens) * nkv * ((max_context + kGroupKeys - 1) / kGroupKeys);
-    long long u = groups / (148LL * 3 * 8);
-    u = u < 1 ? 1 : (u > 16 ? 16 : u);
+    long long u = groups / 1100;
+    u = u < 2 ? 2 : (u > 16 ? 16 : u);
     return static_cast<int>(u) * kGroupKeys;
 }
 

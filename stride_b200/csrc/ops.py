@@ -38,6 +38,8 @@ _SIGNATURES = {
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                                              c_int, c_int, c_void_p]),
+    "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
+                                               c_void_p, c_int, c_void_p, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
@@ -152,13 +154,78 @@ def silu_mul(inp, out) -> None:
 
 
 # ----------------------------------------------------------------------- matmul
+# Up to this many rows (tokens) the bfloat16 product runs on the package's own
+# tcgen05 kernel, which streams the weights once through a TMA ring with the
+# weight rows as the 128-row tile side; above it the library product is called,
+# as the reference's engine does. STRIDE_B200_TC_GEMM=0 switches the kernel off.
+import os as _os
+
+TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 64
+_TC_TICKETS = 8192
+_tc_state: dict = {}
+
+
+def _tc_buffers(device, partial_floats: int):
+    st = _tc_state.get(device)
+    if st is None:
+        st = {"tickets": torch.zeros(_TC_TICKETS, dtype=torch.int32, device=device),
+              "status": torch.zeros(1, dtype=torch.int32, device=device), "partials": None, "retired": []}
+        _tc_state[device] = st
+    if partial_floats and (st["partials"] is None or st["partials"].numel() < partial_floats):
+        if st["partials"] is not None:
+            st["retired"].append(st["partials"])      # a captured graph may still use it
+        st["partials"] = torch.empty(max(partial_floats, 1 << 20), dtype=torch.float32, device=device)
+    return st
+
+
+def _tc_scratch_floats(n_out: int, tokens: int, k: int) -> int:
+    f = _bound.get("stride_gemm_tc_scratch_floats")
+    if f is None:
+        f = build.load_kernel_library("gemm_bf16_tc").stride_gemm_tc_scratch_floats
+        f.argtypes = [c_int, c_int, c_int]
+        f.restype = c_longlong
+        _bound["stride_gemm_tc_scratch_floats"] = f
+    return int(f(n_out, tokens, k))
+
+
+def tc_status(device=None) -> int:
+    """0, or the code of the first bounded wait that ran out inside the tcgen05
+    kernels (1 producer, 2 tensor-core issuer, 3 epilogue). Synchronises."""
+    codes = [int(st["status"].item()) for dev, st in _tc_state.items() if device is None or dev == device]
+    return next((c for c in codes if c), 0)
+
+
+def status_tensor(device):
+    """The device word that the tcgen05 kernels set on a timed-out wait (for callers that copy it with their own results)."""
+    return _tc_buffers(torch.device(device), 0)["status"]
+
+
+def linear_tc(x, weight, out) -> bool:
+    """``out = x @ weight.T`` on the tcgen05 kernel. Returns False when the kernel
+    does not take the shape (the caller then uses the library product)."""
+    m, k = x.shape
+    n = weight.shape[0]
+    st = _tc_buffers(x.device, _tc_scratch_floats(n, m, k))
+    partials = st["partials"]
+    code = _fn("stride_gemm_tc_skinny")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
+                                        m, n, k, int(out.dtype == torch.float32),
+                                        None if partials is None else partials.data_ptr(),
+                                        0 if partials is None else partials.numel(), st["tickets"].data_ptr(), _TC_TICKETS,
+                                        st["status"].data_ptr(), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_tc_skinny")
+    return True
+
+
 def linear(x, weight, out) -> None:
     """``out = x @ weight.T`` for row-major ``weight`` [out_features, in_features].
 
     float32 runs the package's own FMA kernel (true 32-bit, order of the sum
-    fixed). bfloat16 calls the library matrix product, as the reference's engine
-    does (python/stride_worker/model.py:258-260); ``out`` may then be float32 to
-    keep the accumulator's precision (the output head).
+    fixed). bfloat16 with few rows runs the package's tcgen05 kernel; with many
+    rows it calls the library matrix product, as the reference's engine does
+    (python/stride_worker/model.py:258-260). ``out`` may be float32 for bfloat16
+    inputs to keep the accumulator's precision (the output head).
     """
     m, k = x.shape
     n = weight.shape[0]
@@ -170,6 +237,10 @@ def linear(x, weight, out) -> None:
         return
     _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out")
     if m == 0:
+        return
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("linear: the output must be bfloat16 or float32")
+    if m <= TC_GEMM_MAX_TOKENS and linear_tc(x, weight, out):
         return
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)

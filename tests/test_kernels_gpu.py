@@ -397,3 +397,36 @@ def test_prefill_attention_masks_the_future_and_the_far_past(ops):
     no_window = torch.empty_like(out)
     ops.paged_attention_prefill(dev(q), nq * hd, no_window, dev(k_pages), dev(v_pages), *args, 0)
     assert float((no_window.float() - out.float()).abs().max()) > 0.05, "the window changed nothing"
+
+
+# ------------------------------------------------------------- tcgen05 matrix product
+@pytest.mark.parametrize("tokens,n_out,k", [
+    (1, 128, 64), (8, 6144, 4096), (8, 4096, 14336), (16, 136, 4104), (17, 256, 512), (33, 384, 1024), (64, 1000, 4096),
+    (5, 251, 88), (200, 512, 256), (3, 128256, 256),
+])
+def test_tcgen05_product_for_few_tokens(ops, tokens, n_out, k):
+    g = torch.Generator().manual_seed(30)
+    x = torch.randn(tokens, k, generator=g).bfloat16()
+    w = (torch.randn(n_out, k, generator=g) * 0.05).bfloat16()
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((tokens, n_out), 7.0, dtype=out_dtype, device="cuda")
+        for _ in range(2):      # twice: the tickets of a split product must be ready again
+            out.fill_(7.0)
+            assert ops.linear_tc(dev(x), dev(w), out), "the kernel refused a shape it should take"
+            torch.cuda.synchronize()
+            err = float((out.double().cpu() - want).abs().max())
+            assert err <= tol * scale, f"{out_dtype}: max abs error {err:.3e} against scale {scale:.3e}"
+    assert ops.tc_status() == 0
+
+
+def test_tcgen05_product_refuses_what_it_cannot_run(ops):
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda")        # k % 8 != 0
+    w = torch.zeros(128, 100, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_tc(x, w, out)
+    ops.linear(x, w, out)                                                # falls back to the library product
+    big = torch.zeros(300, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_tc(big, torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda"),
+                             torch.zeros(300, 128, dtype=torch.bfloat16, device="cuda"))
