@@ -34,6 +34,8 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
                           int table_width, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions,
                           float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int page_size,
                           float scale_log2e, int window, int split_keys, int num_splits) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
     constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
@@ -237,6 +239,8 @@ __global__ void __launch_bounds__(HD)
 paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                           __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
                           const int32_t* __restrict__ positions, int nq, int window, int split_keys, int num_splits) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float weights[];          // num_splits floats, then 32 for the reductions
     float* scratch = weights + num_splits;
     const int head = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
@@ -304,11 +308,11 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
         configured = true;
     }
     dim3 grid(num_splits, nkv, tokens);
-    paged_decode_split_kernel<HD><<<grid, 128, smem, stream>>>(q, q_stride, k_pages, v_pages, block_table, table_width,
+    stride::launch(paged_decode_split_kernel<HD>, dim3(grid), dim3(128), smem, stream, q, q_stride, k_pages, v_pages, block_table, table_width,
                                                                seq_of_token, positions, part_o, part_ml, nq, nkv, page_size,
                                                                scale * 1.4426950408889634f, window, split_keys, num_splits);
     const int merge_smem = (num_splits + 32) * static_cast<int>(sizeof(float));
-    paged_decode_merge_kernel<HD><<<dim3(nq, tokens), HD, merge_smem, stream>>>(part_o, part_ml, out, seq_of_token, positions,
+    stride::launch(paged_decode_merge_kernel<HD>, dim3(dim3(nq, tokens)), dim3(HD), merge_smem, stream, part_o, part_ml, out, seq_of_token, positions,
                                                                                 nq, window, split_keys, num_splits);
     return STRIDE_LAUNCH_STATUS();
 }

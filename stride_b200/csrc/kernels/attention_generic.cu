@@ -56,6 +56,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
                                const T* __restrict__ v_pages, const int32_t* __restrict__ block_table, int table_width,
                                const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions, int nq,
                                int nkv, int hd, int page_size, float scale, int window) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ __align__(16) float q_smem[kWarps][kMaxHeadDim];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -137,11 +139,11 @@ extern "C" int stride_paged_attention_generic(const void* q, int q_stride, void*
     if (tokens == 0) return 0;
     dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
     if (dtype == STRIDE_DTYPE_F32)
-        paged_attention_generic_kernel<float><<<grid, kWarps * 32, 0, stream>>>(
+        stride::launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const float*>(q), q_stride, static_cast<float*>(out), static_cast<const float*>(k_pages),
             static_cast<const float*>(v_pages), block_table, table_width, seq_of_token, positions, nq, nkv, hd, page_size, scale, window);
     else if (dtype == STRIDE_DTYPE_BF16)
-        paged_attention_generic_kernel<__nv_bfloat16><<<grid, kWarps * 32, 0, stream>>>(
+        stride::launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(kWarps * 32), 0, stream, 
             static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<__nv_bfloat16*>(out),
             static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages), block_table, table_width,
             seq_of_token, positions, nq, nkv, hd, page_size, scale, window);

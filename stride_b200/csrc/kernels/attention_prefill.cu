@@ -26,6 +26,8 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfl
                      const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                      const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
                      int page_size, float scale_log2e, int window) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int ROW_BYTES = HD * 2;
     constexpr int CHUNKS = HD / 8;
     constexpr int KSTEPS = HD / 16;
@@ -237,7 +239,7 @@ int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, con
         configured = true;
     }
     dim3 grid(max_tiles, nq);
-    paged_prefill_kernel<HD><<<grid, 128, smem, stream>>>(q, q_stride, out, k_pages, v_pages, block_table, table_width, q_start,
+    stride::launch(paged_prefill_kernel<HD>, dim3(grid), dim3(128), smem, stream, q, q_stride, out, k_pages, v_pages, block_table, table_width, q_start,
                                                           q_len, ctx_len, num_seqs, nq, nkv, page_size,
                                                           scale * 1.4426950408889634f, window);
     return STRIDE_LAUNCH_STATUS();

@@ -11,6 +11,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #define STRIDE_DTYPE_F32 0
 #define STRIDE_DTYPE_BF16 1
 
@@ -20,6 +22,42 @@
 #define STRIDE_LAUNCH_STATUS() static_cast<int>(cudaPeekAtLastError())
 
 namespace stride {
+
+// ------------------------------------------------ programmatic dependent launch
+// Every kernel of the package is launched with the attribute that lets it start
+// while the kernel before it on the stream is still finishing. A kernel calls
+// pdl_trigger() at once (the next kernel may then be scheduled as soon as SMs
+// have room) and pdl_wait() before it reads or writes anything another kernel
+// touches; pdl_wait() returns when the kernel before it has completed and its
+// writes are visible. What a kernel does before pdl_wait() overlaps the tail of
+// its predecessor: block start-up, barrier and tensor-memory set-up, and, in the
+// matrix products, the first TMA loads of the weights. Launched without the
+// attribute (STRIDE_B200_PDL=0), both calls do nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("STRIDE_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }

@@ -17,6 +17,8 @@ namespace stride {
 template <typename T>
 __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ seq_of_token,
                                     const T* __restrict__ table, float* __restrict__ out, int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const bool live = seq_of_token == nullptr || seq_of_token[t] >= 0;
     int id = ids[t];
@@ -37,6 +39,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int hidden, float eps) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float row_buf[];  // hidden floats, then 32 for the reduction
     float* scratch = row_buf + hidden;
     const int r = blockIdx.x;
@@ -64,6 +68,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 // its hidden state, or a part that asks for the materialised stream).
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (i < n) residual[i] = __fadd_rn(residual[i], to_f32(delta[i]));
 }
@@ -83,6 +89,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd,
                                      int page_size, int rotate) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int heads = nq + 2 * nkv;
@@ -127,6 +135,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
 // silu(z) = z * sigmoid(z) (python/stride_worker/layers.py:161), in float32.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
@@ -181,6 +191,8 @@ template <typename T, int ITERS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const size_t s = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
@@ -247,6 +259,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
                                          const float* __restrict__ cos_table, const float* __restrict__ sin_table,
                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd,
                                          int page_size, int rotate) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int V = Pack<T>::V;
     const int t = blockIdx.x;
     const int half = hd >> 1;
@@ -298,6 +312,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
 // silu_mul_kernel with 16-byte accesses (inter % V == 0).
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t packs) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int V = Pack<T>::V;
     const int per_row = inter / V;
     for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < packs;
@@ -317,6 +333,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ ou
 template <typename T>
 __global__ void embed_gather_vec_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ seq_of_token,
                                         const T* __restrict__ table, float* __restrict__ out, int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int V = Pack<T>::V;
     const int t = blockIdx.x;
     const bool live = seq_of_token == nullptr || seq_of_token[t] >= 0;
@@ -348,14 +366,14 @@ int stride_embed_gather(const int32_t* ids, const int32_t* seq_of_token, const v
     const bool aligned = (reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
     if (dtype == STRIDE_DTYPE_F32) {
         if (aligned && hidden % 4 == 0)
-            embed_gather_vec_kernel<float><<<tokens, 128, 0, stream>>>(ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
+            stride::launch(embed_gather_vec_kernel<float>, dim3(tokens), dim3(128), 0, stream, ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
         else
-            embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
+            stride::launch(embed_gather_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, seq_of_token, static_cast<const float*>(table), out, hidden, vocab);
     } else if (dtype == STRIDE_DTYPE_BF16) {
         if (aligned && hidden % 8 == 0)
-            embed_gather_vec_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>(ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
+            stride::launch(embed_gather_vec_kernel<__nv_bfloat16>, dim3(tokens), dim3(128), 0, stream, ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
         else
-            embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
+            stride::launch(embed_gather_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, seq_of_token, static_cast<const __nv_bfloat16*>(table), out, hidden, vocab);
     } else {
         return STRIDE_BAD_ARGUMENT;
     }
@@ -375,7 +393,7 @@ int stride_add_rmsnorm(float* residual, const void* delta, const float* weight, 
             const int threads = quads <= 32 ? 32 : (quads <= 64 ? 64 : (quads <= 128 ? 128 : 256));
             const int iters = (quads + threads - 1) / threads;
 #define STRIDE_NORM_LAUNCH(T, I)                                                                                            \
-    add_rmsnorm_vec_kernel<T, I><<<num_rows, threads, 0, stream>>>(residual, static_cast<const T*>(delta), weight,         \
+    stride::launch(add_rmsnorm_vec_kernel<T, I>, dim3(num_rows), dim3(threads), 0, stream, residual, static_cast<const T*>(delta), weight,         \
                                                                    static_cast<T*>(out), rows, hidden, eps)
 #define STRIDE_NORM_DISPATCH(T)                                                                                             \
     do {                                                                                                                   \
@@ -396,10 +414,10 @@ int stride_add_rmsnorm(float* residual, const void* delta, const float* weight, 
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (dtype == STRIDE_DTYPE_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        add_rmsnorm_kernel<float><<<num_rows, threads, smem, stream>>>(residual, static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
+        stride::launch(add_rmsnorm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, residual, static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
     } else if (dtype == STRIDE_DTYPE_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        add_rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, smem, stream>>>(residual, static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
+        stride::launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual, static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
     } else {
         return STRIDE_BAD_ARGUMENT;
     }
@@ -411,9 +429,9 @@ int stride_add_residual(float* residual, const void* delta, long long n, int dty
     if (n == 0) return 0;
     const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
     if (dtype == STRIDE_DTYPE_F32)
-        add_residual_kernel<float><<<blocks, 256, 0, stream>>>(residual, static_cast<const float*>(delta), static_cast<size_t>(n));
+        stride::launch(add_residual_kernel<float>, dim3(blocks), dim3(256), 0, stream, residual, static_cast<const float*>(delta), static_cast<size_t>(n));
     else if (dtype == STRIDE_DTYPE_BF16)
-        add_residual_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(residual, static_cast<const __nv_bfloat16*>(delta), static_cast<size_t>(n));
+        stride::launch(add_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, residual, static_cast<const __nv_bfloat16*>(delta), static_cast<size_t>(n));
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();
@@ -434,16 +452,16 @@ int stride_rope_kv_write(void* qkv, const float* bias, const int32_t* positions,
             const int units = work / vec;
             const int vthreads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
             if (dtype == STRIDE_DTYPE_F32)
-                rope_kv_write_vec_kernel<float><<<tokens, vthreads, 0, stream>>>(static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
+                stride::launch(rope_kv_write_vec_kernel<float>, dim3(tokens), dim3(vthreads), 0, stream, static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
             else
-                rope_kv_write_vec_kernel<__nv_bfloat16><<<tokens, vthreads, 0, stream>>>(static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
+                stride::launch(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(tokens), dim3(vthreads), 0, stream, static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
             return STRIDE_LAUNCH_STATUS();
         }
     }
     if (dtype == STRIDE_DTYPE_F32)
-        rope_kv_write_kernel<float><<<tokens, threads, 0, stream>>>(static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
+        stride::launch(rope_kv_write_kernel<float>, dim3(tokens), dim3(threads), 0, stream, static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
     else if (dtype == STRIDE_DTYPE_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
+        stride::launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();
@@ -461,16 +479,16 @@ int stride_silu_mul(const void* in, void* out, int tokens, int inter, int dtype,
             const size_t packs = total / vec;
             const unsigned vblocks = static_cast<unsigned>(std::min<size_t>((packs + 255) / 256, 148 * 16));
             if (dtype == STRIDE_DTYPE_F32)
-                silu_mul_vec_kernel<float><<<vblocks, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), inter, packs);
+                stride::launch(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, packs);
             else
-                silu_mul_vec_kernel<__nv_bfloat16><<<vblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, packs);
+                stride::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, packs);
             return STRIDE_LAUNCH_STATUS();
         }
     }
     if (dtype == STRIDE_DTYPE_F32)
-        silu_mul_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), inter, total);
+        stride::launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, total);
     else if (dtype == STRIDE_DTYPE_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, total);
+        stride::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, total);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

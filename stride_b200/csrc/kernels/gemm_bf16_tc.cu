@@ -124,7 +124,7 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
 
 // D tile rows are rows of A, columns are rows of B. TRANSPOSED: out[col * ldo + row]
 // (swapped use: rows are output features, columns tokens); else out[row * ldo + col].
-template <int BLOCK_N, int STAGES, bool TRANSPOSED, typename OutT>
+template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out,
                     int ldo, int M, int N, int K, int k_blocks_per_split, float* __restrict__ partials,
@@ -141,6 +141,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ uint32_t tmem_base_slot;
     __shared__ int last_flag;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * kBlockM, n0 = blockIdx.y * BLOCK_N;
     const int total_k_blocks = (K + kBlockK - 1) / kBlockK;
@@ -164,9 +165,19 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: one thread feeds the ring
-            int armed = 0;
-            for (int i = 0; i < num_kb; ++i) {
+            // ---- producer: one thread feeds the ring. The A operand (the weights, when the
+            // product is used swapped) is written by no kernel of the step, so its first
+            // ring of tiles is requested before waiting for the kernel that produces B.
+            const int early = A_INDEPENDENT ? min(num_kb, STAGES) : 0;
+            for (int i = 0; i < early; ++i) {
+                const uint32_t bar = smem_u32(&full_bar[i]);
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_a, bar, (kb_begin + i) * kBlockK, m0);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_b, smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, n0);
+            for (int i = early; i < num_kb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / STAGES) & 1) ^ 1, status, 1)) break;
                 const uint32_t bar = smem_u32(&full_bar[s]);
@@ -174,9 +185,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES);
                 tma_load_2d(a_dst, &map_a, bar, (kb_begin + i) * kBlockK, m0);
                 tma_load_2d(a_dst + A_BYTES, &map_b, bar, (kb_begin + i) * kBlockK, n0);
-                armed = i + 1;
             }
-            (void)armed;
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -205,6 +214,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int row = quad * 32 + lane;                  // row of the tile this thread holds
         const bool ok = mbar_wait(smem_u32(&done_bar), 0, status, 3);
         tc_fence_after();
+        pdl_wait();        // returns at once here (the producer passed it long ago); keeps this thread's stores ordered too
         const bool split = gridDim.z > 1;
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         float* my_partial = split ? partials + ((static_cast<size_t>(blockIdx.z) * gridDim.x * gridDim.y + tile) * kBlockM + row) * BLOCK_N
@@ -335,7 +345,7 @@ int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ld
            float* partials, int* tickets, int* status, cudaStream_t stream) {
     constexpr int smem = STAGES * (kBlockM * kBlockK * 2 + BLOCK_N * kBlockK * 2) + 1024;
     static bool configured = false;
-    auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, OutT>;
+    auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, TRANSPOSED, OutT>;   // swapped use: A holds weights
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -344,7 +354,7 @@ int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ld
     const int k_blocks = (K + kBlockK - 1) / kBlockK;
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((M + kBlockM - 1) / kBlockM, (N + BLOCK_N - 1) / BLOCK_N, splits);
-    kernel<<<grid, kThreads, smem, stream>>>(*map_a, *map_b, out, ldo, M, N, K, per_split, partials, tickets, status);
+    stride::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, *map_a, *map_b, out, ldo, M, N, K, per_split, partials, tickets, status);
     return STRIDE_LAUNCH_STATUS();
 }
 

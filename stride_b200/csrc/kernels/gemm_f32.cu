@@ -15,6 +15,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                           float* __restrict__ C, int M, int N, int K, int lda, int ldw,
                                                           int ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -65,6 +67,6 @@ extern "C" int stride_gemm_nt_f32(const float* A, const float* W, float* C, int 
     if (M == 0) return 0;
     dim3 grid((N + stride::BN - 1) / stride::BN, (M + stride::BM - 1) / stride::BM);
     if (grid.y > 65535) return STRIDE_UNSUPPORTED;
-    stride::gemm_nt_f32_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    stride::launch(stride::gemm_nt_f32_kernel, dim3(grid), dim3(256), 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
     return STRIDE_LAUNCH_STATUS();
 }

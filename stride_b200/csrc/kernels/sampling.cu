@@ -21,6 +21,8 @@ __device__ __forceinline__ float masked_logit(const float* row, int i, int banne
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_stride, const float* __restrict__ temperature,
                    const float* __restrict__ uniform, const int32_t* __restrict__ suppress, int32_t* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float s_val[kSampleThreads];
     __shared__ int s_idx[kSampleThreads];
     __shared__ float scratch[32];
@@ -111,6 +113,6 @@ extern "C" int stride_sample_rows(const float* logits, int rows, int vocab, long
     if (rows < 0 || vocab <= 0 || row_stride < vocab) return STRIDE_BAD_ARGUMENT;
     if (temperature != nullptr && uniform == nullptr) return STRIDE_BAD_ARGUMENT;
     if (rows == 0) return 0;
-    stride::sample_rows_kernel<<<rows, stride::kSampleThreads, 0, stream>>>(logits, vocab, row_stride, temperature, uniform, suppress, out);
+    stride::launch(stride::sample_rows_kernel, dim3(rows), dim3(stride::kSampleThreads), 0, stream, logits, vocab, row_stride, temperature, uniform, suppress, out);
     return STRIDE_LAUNCH_STATUS();
 }
