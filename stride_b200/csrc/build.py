@@ -35,7 +35,11 @@ KERNEL_DIR = os.path.join(HERE, "kernels")
 RUNTIME_DIR = os.path.join(HERE, "runtime")
 
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3"]
+# -fno-gnu-unique: function-local statics of templates (such as "this kernel's attributes are set")
+# must belong to one library; as GNU unique symbols they would be shared by every library that
+# instantiates the same template, although each library carries its own copy of the kernel.
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
+              "-Xcompiler", "-fno-gnu-unique"]
 CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
 
 
@@ -157,7 +161,13 @@ def build_kernel_library(name: str) -> str:
     def cmd(out):
         return [find_nvcc(), *NVCC_ARCH, *NVCC_FLAGS, *extra, "-I", KERNEL_DIR, "-o", out, src, "-lcuda"]
 
-    return _build(f"kernels_{name}", [src], _headers(KERNEL_DIR), cmd)
+    deps = _headers(KERNEL_DIR)
+    with open(src) as f:     # a source may include another source (a variant that reuses its kernels)
+        for line in f:
+            line = line.strip()
+            if line.startswith('#include "') and line.split('"')[1].endswith(".cu"):
+                deps.append(os.path.join(KERNEL_DIR, line.split('"')[1]))
+    return _build(f"kernels_{name}", [src], deps, cmd)
 
 
 def build_runtime() -> str:

@@ -160,7 +160,7 @@ def silu_mul(inp, out) -> None:
 # as the reference's engine does. STRIDE_B200_TC_GEMM=0 switches the kernel off.
 import os as _os
 
-TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 64
+TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 16
 _TC_TICKETS = 8192
 _tc_state: dict = {}
 
