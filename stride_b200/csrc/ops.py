@@ -161,6 +161,7 @@ def silu_mul(inp, out) -> None:
 import os as _os
 
 TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 16
+_TC_MAX_WEIGHT_BYTES = int(float(_os.environ.get("STRIDE_TC_MAX_WEIGHT_MB", "1e9")) * 1e6)
 _TC_TICKETS = 8192
 _tc_state: dict = {}
 
@@ -240,7 +241,7 @@ def linear(x, weight, out) -> None:
         return
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the output must be bfloat16 or float32")
-    if m <= TC_GEMM_MAX_TOKENS and linear_tc(x, weight, out):
+    if m <= TC_GEMM_MAX_TOKENS and n * k * 2 <= _TC_MAX_WEIGHT_BYTES and linear_tc(x, weight, out):
         return
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)

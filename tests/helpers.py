@@ -79,8 +79,34 @@ TINY_C = {
     "hidden_act": "silu",
 }
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
+# Head size 128 and a group of 4, the sizes that the tensor-core attention kernels and the
+# tcgen05 matrix product take, so that whole-model runs go through them too.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 2,
+    "hidden_size": 192,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "head_dim": 128,
+    "intermediate_size": 320,
+    "vocab_size": 515,
+    "rope_theta": 500000.0,
+    "rope_scaling": {
+        "rope_type": "llama3",
+        "factor": 8.0,
+        "low_freq_factor": 1.0,
+        "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 128,
+    },
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 2048,
+    "hidden_act": "silu",
+}
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 def geometry(cfg: dict):

@@ -18,10 +18,10 @@ from helpers import PAGE_SIZE, TINY, compare_logits, read_model_dir, seeded_stat
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LENGTHS = {"a": 70, "b": 33, "c": 161, "d": 17, "e": 2, "f": 64}
+LENGTHS = {"a": 70, "b": 33, "c": 161, "d": 17, "e": 2, "f": 64, "g": 230}
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def case(request, tmp_models):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
