@@ -46,6 +46,9 @@ _SIGNATURES = {
     "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                              c_int, c_float, c_int, c_void_p]),
+    "stride_paged_prefill_attention_tc": ("attention_prefill_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                                   c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
@@ -161,7 +164,11 @@ def silu_mul(inp, out) -> None:
 import os as _os
 
 TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 16
-_TC_MAX_WEIGHT_BYTES = int(float(_os.environ.get("STRIDE_TC_MAX_WEIGHT_MB", "1e9")) * 1e6)
+# ... and only for weight matrices with at least this many 128-row tiles: with fewer, the K range has to be
+# split over several CTAs and the partial-tile round trip makes the kernel slower than the library's inside
+# the decode step (measured: QKV and down lose 3-4 us each, gate/up and the head gain). STRIDE_TC_MIN_TILES=0
+# sends every product of up to TC_GEMM_MAX_TOKENS rows to the kernel.
+TC_GEMM_MIN_TILES = int(_os.environ.get("STRIDE_TC_MIN_TILES", "100"))
 _TC_TICKETS = 8192
 _tc_state: dict = {}
 
@@ -241,7 +248,7 @@ def linear(x, weight, out) -> None:
         return
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the output must be bfloat16 or float32")
-    if m <= TC_GEMM_MAX_TOKENS and n * k * 2 <= _TC_MAX_WEIGHT_BYTES and linear_tc(x, weight, out):
+    if m <= TC_GEMM_MAX_TOKENS and -(-n // 128) >= TC_GEMM_MIN_TILES and linear_tc(x, weight, out):
         return
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
@@ -294,6 +301,29 @@ def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table,
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
         int(max_context), _stream()), "paged_attention_decode")
     counters["launches"] += 1       # the launcher runs two kernels
+
+
+TC_ATTENTION = _os.environ.get("STRIDE_B200_TC_ATTENTION", "1") != "0"
+
+
+def paged_attention_prefill_tc(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,
+                               nq: int, nkv: int, hd: int, page_size: int, scale: float, window: int) -> bool:
+    """The tcgen05 version of ``paged_attention_prefill`` (same arguments). Returns False
+    when it does not take the sizes; the caller then uses the mma.sync kernel."""
+    tokens = out.shape[0]
+    if out.shape[1] != nq * hd:
+        raise KernelError("attention output has the wrong width")
+    st = _tc_buffers(q.device, 0)
+    code = _fn("stride_paged_prefill_attention_tc")(
+        _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
+        _dev(ctx_len, "ctx_len", torch.int32), num_seqs, tokens, nq, nkv, hd, page_size, float(scale), int(window),
+        st["status"].data_ptr(), _stream())
+    if code == -2:
+        return False
+    _check(code, "paged_attention_prefill_tc")
+    return True
 
 
 def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table, q_start, q_len, ctx_len, num_seqs: int,

@@ -93,8 +93,11 @@ class PagedAttention(Mixer):
             return
         split = min(ctx.decode_tail_start, tokens)          # portions before, single decoded tokens after
         if split > 0:
-            ops.paged_attention_prefill(qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table,
-                                        ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.decode_tail_seq, *geometry)
+            args = (qkv[:split], self.qkv_dim, attn[:split], cache.k_pages, cache.v_pages, table, ctx.q_start, ctx.q_len,
+                    ctx.ctx_len, ctx.decode_tail_seq, *geometry)
+            # tcgen05 kernel first; the mma.sync kernel takes what it refuses (odd page sizes)
+            if not (ops.TC_ATTENTION and ops.paged_attention_prefill_tc(*args)):
+                ops.paged_attention_prefill(*args)
         if tokens > split:
             n = tokens - split
             scratch = self.rt.scratch("attention_splits", ops.decode_scratch_floats(n, self.nq, self.nkv, self.hd, ctx.context_bound))

@@ -430,3 +430,46 @@ def test_tcgen05_product_refuses_what_it_cannot_run(ops):
     big = torch.zeros(300, 64, dtype=torch.bfloat16, device="cuda")
     assert not ops.linear_tc(big, torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda"),
                              torch.zeros(300, 128, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [
+    (8, 2, 128, 16, None), (3, 1, 64, 8, None), (4, 4, 128, 32, None), (8, 2, 128, 16, 70), (6, 2, 64, 16, 5), (4, 1, 128, 16, 64),
+    (2, 1, 128, 128, None), (4, 2, 128, 64, 300),
+])
+def test_prefill_attention_on_tcgen05(ops, nq, nkv, hd, page, window):
+    g = torch.Generator().manual_seed(23)
+    dtype = torch.bfloat16
+    # whole prompts across several 128-key tiles, portions that start inside a page or a tile, tiny portions, one token
+    seqs = [(0, 300), (0, 128), (0, 129), (100, 37), (64, 2), (333, 260), (5, 1), (0, 1), (128, 127), (250, 10)]
+    q, k_pages, v_pages, table, _seq_of, _pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, window, spike=(None, 2))
+    # poison every key and value slot that no request owns: stale contents must never reach a result
+    used = torch.zeros(k_pages.shape[0], page, dtype=torch.bool)
+    for s, (ctx, new) in enumerate(seqs):
+        for p in range(-(-(ctx + new) // page)):
+            n = min(page, ctx + new - p * page)
+            used[int(table[s, p]), :n] = True
+    k_pages = k_pages.clone()
+    v_pages = v_pages.clone()
+    k_pages.transpose(1, 2)[~used] = float("nan")
+    v_pages.transpose(1, 2)[~used] = float("nan")
+    q_start, q_len, ctx_len = _seq_arrays(seqs)
+    out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+    took = ops.paged_attention_prefill_tc(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                          dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, window or 0)
+    assert took, "the kernel refused sizes it should take"
+    torch.cuda.synchronize()
+    assert ops.tc_status() == 0
+    close(out, want, dtype)
+    mma = torch.empty_like(out)
+    ops.paged_attention_prefill(dev(q), nq * hd, mma, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, window or 0)
+    close(out, mma.float(), dtype)
+
+
+def test_prefill_attention_on_tcgen05_refuses_odd_page_sizes(ops):
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda")
+    pages = torch.zeros(2, 1, 24, 128, dtype=torch.bfloat16, device="cuda")
+    table = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    assert not ops.paged_attention_prefill_tc(q, 128, torch.empty_like(q), pages, pages, table, z, z + 4, z + 4, 1, 1, 1, 128, 24,
+                                              0.1, 0)
