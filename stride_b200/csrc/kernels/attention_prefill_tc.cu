@@ -1,11 +1,14 @@
 // Prefill attention in bfloat16 on the fifth-generation tensor cores.
 //
-// One CTA owns 128 consecutive query rows of one request and one query head.
-// Keys and values are walked in tiles of 128. For each tile
-//   S = Q K^T        tcgen05.mma, M = 128 queries, N = 128 keys, accumulator in tensor memory
+// One CTA owns 128 consecutive query rows of one request and one query head; two CTAs share
+// an SM, so that one's softmax overlaps the other's products. Keys and values are walked in
+// tiles of 64. For each tile
+//   S = Q K^T        tcgen05.mma, M = 128 queries, N = 64 keys, accumulator in tensor memory
 //   P = softmax part four warps, one thread per query row, read S with tcgen05.ld, keep the
-//                    running maximum and sum in float32, write P (bfloat16) to shared memory
-//   O += P V         tcgen05.mma, N = head size, V taken MN-major straight from the cache layout
+//                    running maximum and sum in float32, write P (bfloat16 pairs) back into
+//                    tensor memory over S with tcgen05.st
+//   O += P V         tcgen05.mma with A = P from tensor memory, N = head size, V taken MN-major
+//                    straight from the cache layout
 // Q, K and V arrive by TMA: Q as a 128-row box of the projection output, K and V page by page
 // through the request's block table (a page's keys of one head are contiguous in the cache, so
 // a page is one box per 64 columns). The output accumulator is rescaled only when a row's
@@ -21,28 +24,27 @@ namespace stride {
 namespace tc {
 
 constexpr int kQRows = 128;
-constexpr int kKeys = 128;
+constexpr int kKeys = 64;
 constexpr int kAttnThreads = 192;
 constexpr float kRescaleThreshold = 8.f;      // in log2 units
 
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                        const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
                        int page_size, float scale_log2e, int window, int* __restrict__ status) {
     constexpr int HALVES = HD / 64;                       // 64-column boxes per row
-    constexpr int HALF_BYTES = 128 * 128;                 // a [128 rows x 64 columns] bf16 box
+    constexpr int HALF_BYTES = kQRows * 128;              // a [128 rows x 64 columns] bf16 box of Q
+    constexpr int KV_HALF_BYTES = kKeys * 128;            // a [64 keys x 64 columns] box of K or V
     constexpr int Q_BYTES = HALVES * HALF_BYTES;
-    constexpr int KV_BYTES = HALVES * HALF_BYTES;          // one K tile or one V tile
-    constexpr int P_BYTES = 2 * HALF_BYTES;
-    constexpr uint32_t TMEM_COLS = 256;                   // S: 128 columns, O: HD columns
+    constexpr int KV_BYTES = HALVES * KV_HALF_BYTES;      // one K tile or one V tile
+    constexpr uint32_t TMEM_COLS = 256;                   // S (and P over it): 64 columns, O: HD columns
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_s = smem;
     unsigned char* kv_s = q_s + Q_BYTES;                  // stage st: K at kv_s + st * 2 * KV_BYTES, V right after it
-    unsigned char* p_s = kv_s + 4 * KV_BYTES;
     __shared__ __align__(8) uint64_t q_full, s_full, p_full, pv_done;
     __shared__ __align__(8) uint64_t kv_full[2], kv_empty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -120,8 +122,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!(lo <= last_pos && lo + page_size > first_key)) continue;
                     const int y = (table[lo / page_size] * nkv + kvh) * page_size;
                     for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(smem_u32(k_dst + h * HALF_BYTES) + i * page_bytes, &map_k, bar, h * 64, y);
-                        tma_load_2d(smem_u32(v_dst + h * HALF_BYTES) + i * page_bytes, &map_v, bar, h * 64, y);
+                        tma_load_2d(smem_u32(k_dst + h * KV_HALF_BYTES) + i * page_bytes, &map_k, bar, h * 64, y);
+                        tma_load_2d(smem_u32(v_dst + h * KV_HALF_BYTES) + i * page_bytes, &map_v, bar, h * 64, y);
                     }
                 }
             }
@@ -140,19 +142,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const uint32_t k_addr = smem_u32(kv_s + st * 2 * KV_BYTES), v_addr = k_addr + KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {      // S = Q K^T, 16 head columns per product
-                    const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-                    umma_bf16(tmem_s, smem_desc(smem_u32(q_s) + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk,
-                              kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_s, smem_desc(smem_u32(q_s) + (kk / 4) * HALF_BYTES + (kk % 4) * 32, 16, 1024),
+                              smem_desc(k_addr + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&s_full));
                 ok = mbar_wait(smem_u32(&p_full), static_cast<uint32_t>(j) & 1u, status, 14);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < kKeys / 16; ++ks) {   // O += P V, 16 keys per product; V is MN-major
-                    const uint32_t p_off = (ks / 4) * HALF_BYTES + (ks % 4) * 32;
-                    umma_bf16(tmem_o, smem_desc(smem_u32(p_s) + p_off, 16, 1024), smem_desc(v_addr + ks * 2048, HALF_BYTES, 1024),
-                              idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < kKeys / 16; ++ks) {   // O += P V, 16 keys per product: P from tensor memory
+                    // (16 bfloat16 = 8 columns per step), V MN-major: 64-column chunks KV_HALF_BYTES apart
+                    umma_bf16_tmem_a(tmem_o, tmem_s + ks * 8, smem_desc(v_addr + ks * 2048, KV_HALF_BYTES, 1024), idesc_pv,
+                                     (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&kv_empty[st]));        // keys and values of this stage may be replaced
                 umma_commit(smem_u32(&pv_done));             // O holds this tile; P may be overwritten
@@ -173,6 +174,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) break;
             tc_fence_after();
             const bool edge = k0 + kKeys - 1 > pos0 || (window > 0 && k0 <= last_pos - window);   // some (row, key) is masked
+            float sv[kKeys];
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < kKeys / 32; ++c) {
@@ -182,10 +184,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = 0; i < 32; ++i) {
                     const int key = k0 + c * 32 + i;
                     const bool allowed = !edge || (key <= pos_r && (window <= 0 || key > pos_r - window));
-                    mx = fmaxf(mx, allowed ? v[i] * scale_log2e : -INFINITY);
+                    sv[c * 32 + i] = allowed ? v[i] * scale_log2e : -INFINITY;
+                    mx = fmaxf(mx, sv[c * 32 + i]);
                 }
             }
-            // P and O belong to the previous tile's product until it has finished
+            // P (over S) and O belong to the previous tile's product until it has finished
             if (j > 0) {
                 ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(j - 1) & 1u, status, 16);
                 if (!ok) break;
@@ -207,44 +210,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
             }
+            {
+                float packed[kKeys / 2];       // bfloat16 pairs, carried as 32-bit words
 #pragma unroll
-            for (int c = 0; c < kKeys / 32; ++c) {
-                float v[32];
-                tmem_ld32(tmem_s + lane_base + c * 32, v);
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int key = k0 + c * 32 + i + e;
-                        const bool allowed = !edge || (key <= pos_r && (window <= 0 || key > pos_r - window));
-                        p[e] = allowed ? exp2f(v[i + e] * scale_log2e - m_ref) : 0.f;
-                        l += p[e];
-                    }
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p[0], p[1]);
-                    packed[i / 2] = *reinterpret_cast<uint32_t*>(&b);
+                for (int i = 0; i < kKeys; i += 2) {
+                    // a masked score is -inf and gives exactly 0; a row that has seen no key yet has m_ref = -inf
+                    const float p0 = sv[i] == -INFINITY ? 0.f : exp2f(sv[i] - m_ref);
+                    const float p1 = sv[i + 1] == -INFINITY ? 0.f : exp2f(sv[i + 1] - m_ref);
+                    l += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    packed[i / 2] = __uint_as_float(*reinterpret_cast<uint32_t*>(&b));
                 }
-                // keys c*32 .. c*32+31 of this row: half c/2, 16-byte chunks (c%2)*4 .. +3, XOR-swizzled by the row
-                unsigned char* p_row = p_s + (c / 2) * HALF_BYTES + row * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c % 2) * 4 + q4;
-                    *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-                }
+                tmem_st32(tmem_s + lane_base, packed);
             }
             // Key rows that no query of this tile may see can hold anything (a page never written, the
             // rest of a page): clear their values, or 0 * garbage would poison the product.
             if (k0 + kKeys - 1 > last_pos || k0 < first_key) {
                 const int key = k0 + row;
-                if (key > last_pos || key < first_key) {
+                if (row < kKeys && (key > last_pos || key < first_key)) {
                     unsigned char* v_row = kv_s + st * 2 * KV_BYTES + KV_BYTES + row * 128;
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h)
 #pragma unroll
                         for (int ch = 0; ch < 8; ++ch)
-                            *reinterpret_cast<uint4*>(v_row + h * HALF_BYTES + ch * 16) = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4*>(v_row + h * KV_HALF_BYTES + ch * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
             fence_proxy_async();
@@ -287,7 +276,7 @@ int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtens
                 const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
                 int num_seqs, int max_tiles, int nq, int nkv, int page_size, float scale, int window, int* status,
                 cudaStream_t stream) {
-    constexpr int smem = (HD / 64) * 128 * 128 * 5 + 2 * 128 * 128 + 1024;      // Q, two stages of K and V, P
+    constexpr int smem = (HD / 64) * (kQRows * 128 + 4 * kKeys * 128) + 1024;      // Q, two stages of K and V
     static bool configured = false;
     auto kernel = attn_prefill_tc_kernel<HD>;
     if (!configured) {
@@ -308,7 +297,7 @@ using namespace stride;
 // Attention for the first `num_seqs` requests of the step, which own the first `tokens` rows of
 // the flat batch. q: [tokens, q_stride] bf16 (head h at columns h*hd); out: [tokens, nq*hd];
 // pages: [num_pages, nkv, page_size, hd]. Returns -2 for what it does not take (head sizes other
-// than 64 and 128, page sizes that are not 8, 16, 32, 64 or 128, unaligned strides); the caller
+// than 64 and 128, page sizes that are not 8, 16, 32 or 64, unaligned strides); the caller
 // then uses the mma.sync kernel.
 extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                                  int num_pages, const int32_t* block_table, int table_width,
@@ -318,7 +307,7 @@ extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, vo
     if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || num_pages <= 0)
         return STRIDE_BAD_ARGUMENT;
     if (nq % nkv || status == nullptr) return STRIDE_BAD_ARGUMENT;
-    if ((hd != 64 && hd != 128) || page_size % 8 || 128 % page_size || q_stride % 8 || nq > 65535) return STRIDE_UNSUPPORTED;
+    if ((hd != 64 && hd != 128) || page_size % 8 || tc::kKeys % page_size || q_stride % 8 || nq > 65535) return STRIDE_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_pages) |
          reinterpret_cast<uintptr_t>(v_pages)) % 16)
         return STRIDE_UNSUPPORTED;
