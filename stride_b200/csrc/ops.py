@@ -40,6 +40,7 @@ _SIGNATURES = {
                                                              c_int, c_int, c_void_p]),
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
+    "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
@@ -169,6 +170,9 @@ TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" els
 # the decode step (measured: QKV and down lose 3-4 us each, gate/up and the head gain). STRIDE_TC_MIN_TILES=0
 # sends every product of up to TC_GEMM_MAX_TOKENS rows to the kernel.
 TC_GEMM_MIN_TILES = int(_os.environ.get("STRIDE_TC_MIN_TILES", "100"))
+# Smaller matrices at up to TC_GEMM_MAX_TOKENS rows go to the weight-streaming kernel, which needs no split of K
+# across CTAs. STRIDE_B200_STREAM_GEMM=0 sends them to the library product instead.
+STREAM_GEMM = _os.environ.get("STRIDE_B200_STREAM_GEMM", "1") != "0"
 _TC_TICKETS = 8192
 _tc_state: dict = {}
 
@@ -226,14 +230,29 @@ def linear_tc(x, weight, out) -> bool:
     return True
 
 
+def linear_stream(x, weight, out) -> bool:
+    """``out = x @ weight.T`` on the weight-streaming kernel (at most 16 rows of ``x``).
+    Returns False when the kernel does not take the shape."""
+    m, k = x.shape
+    n = weight.shape[0]
+    code = _fn("stride_gemm_stream_bf16")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
+                                          m, n, k, int(out.dtype == torch.float32), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_stream_bf16")
+    return True
+
+
 def linear(x, weight, out) -> None:
     """``out = x @ weight.T`` for row-major ``weight`` [out_features, in_features].
 
     float32 runs the package's own FMA kernel (true 32-bit, order of the sum
-    fixed). bfloat16 with few rows runs the package's tcgen05 kernel; with many
-    rows it calls the library matrix product, as the reference's engine does
-    (python/stride_worker/model.py:258-260). ``out`` may be float32 for bfloat16
-    inputs to keep the accumulator's precision (the output head).
+    fixed). bfloat16 with few rows (decode steps) runs the package's own kernels:
+    the tcgen05 kernel for large matrices, the weight-streaming kernel for the
+    others; with many rows it calls the library matrix product, as the
+    reference's engine does (python/stride_worker/model.py:258-260). ``out`` may
+    be float32 for bfloat16 inputs to keep the accumulator's precision (the
+    output head).
     """
     m, k = x.shape
     n = weight.shape[0]
@@ -248,8 +267,12 @@ def linear(x, weight, out) -> None:
         return
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("linear: the output must be bfloat16 or float32")
-    if m <= TC_GEMM_MAX_TOKENS and -(-n // 128) >= TC_GEMM_MIN_TILES and linear_tc(x, weight, out):
-        return
+    if m <= TC_GEMM_MAX_TOKENS:
+        if -(-n // 128) >= TC_GEMM_MIN_TILES:
+            if linear_tc(x, weight, out):
+                return
+        elif STREAM_GEMM and linear_stream(x, weight, out):
+            return
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
     else:

@@ -399,6 +399,34 @@ def test_prefill_attention_masks_the_future_and_the_far_past(ops):
     assert float((no_window.float() - out.float()).abs().max()) > 0.05, "the window changed nothing"
 
 
+# ------------------------------------------------- weight-streaming product (decode)
+@pytest.mark.parametrize("tokens,n_out,k", [
+    (1, 16, 8), (8, 4096, 4096), (7, 4096, 14336), (16, 136, 4104), (9, 251, 88), (3, 515, 192), (12, 6144, 1000), (5, 33, 2056),
+])
+def test_streaming_product_for_few_tokens(ops, tokens, n_out, k):
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(tokens, k, generator=g).bfloat16()
+    w = (torch.randn(n_out, k, generator=g) * 0.05).bfloat16()
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((tokens + 1, n_out), 7.0, dtype=out_dtype, device="cuda")
+        assert ops.linear_stream(dev(x), dev(w), out[:tokens]), "the kernel refused a shape it should take"
+        torch.cuda.synchronize()
+        err = float((out[:tokens].double().cpu() - want).abs().max())
+        assert err <= tol * scale, f"{out_dtype}: max abs error {err:.3e} against scale {scale:.3e}"
+        assert float(out[tokens].min()) == 7.0, "the kernel wrote past the last token"
+
+
+def test_streaming_product_refuses_what_it_cannot_run(ops):
+    w = torch.zeros(128, 100, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_stream(torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda"), w,
+                                 torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda"))                 # k % 8 != 0
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_stream(torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda"), w,
+                                 torch.zeros(17, 128, dtype=torch.bfloat16, device="cuda"))                # more than 16 tokens
+
+
 # ------------------------------------------------------------- tcgen05 matrix product
 @pytest.mark.parametrize("tokens,n_out,k", [
     (1, 128, 64), (8, 6144, 4096), (8, 4096, 14336), (16, 136, 4104), (17, 256, 512), (33, 384, 1024), (64, 1000, 4096),
