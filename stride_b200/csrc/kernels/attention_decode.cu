@@ -7,14 +7,19 @@
 // (split, key head, token), multiplies the whole query group of that key head
 // (nq / nkv heads, padded to the 16 rows of an m16n8k16 tile) with its keys on
 // the tensor cores, keeps an online softmax in float32, and writes an
-// unnormalised partial result. A second kernel merges the splits of each
-// (token, query head). Each warp walks its own 16-key tiles through a private
-// two-stage cp.async ring (no block-wide barrier inside the loop), so every
-// resident CTA always has copies in flight while it computes.
+// unnormalised partial result. The CTAs of one (token, key head) count themselves
+// off on a ticket; the one that arrives last merges the splits of the group's
+// query heads and writes the output, so there is no second kernel. Each warp walks
+// its own 16-key tiles through a private two-stage cp.async ring (no block-wide
+// barrier inside the loop), so every resident CTA always has copies in flight
+// while it computes. A CTA whose keys do not include the token's own position
+// starts its first copies before it waits for the kernel before it: those keys
+// were written by earlier steps, only the query and the newest key are new.
 //
 // The rule is that of python/stride_worker/layers.py:109-149 for a single query
 // at position p: keys j <= p (and j > p - window), softmax(q k^T * scale) v, query
-// head h reading key head h / (nq / nkv). Scratch: part_o[token][head][split][hd]
+// head h reading key head h / (nq / nkv). Scratch: kTicketInts ticket counters (zero
+// before the first launch; every launch leaves them zero), part_o[token][head][split][hd]
 // and part_ml[token][head][split][2] (running maximum in the log2 domain, sum).
 #include <cstdlib>
 
@@ -26,16 +31,18 @@ namespace stride {
 constexpr int kTileKeys = 16;     // keys one warp works on at a time
 constexpr int kGroupKeys = 64;    // keys the four warps of a CTA cover per pipeline stage
 constexpr int kStages = 2;
+constexpr int kTicketInts = 65536;   // ticket counters at the start of the scratch, one per (token, key head)
 
 template <int HD>
 __global__ void __launch_bounds__(128)
 paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_pages,
                           const __nv_bfloat16* __restrict__ v_pages, const int32_t* __restrict__ block_table,
                           int table_width, const int32_t* __restrict__ seq_of_token, const int32_t* __restrict__ positions,
-                          float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int page_size,
-                          float scale_log2e, int window, int split_keys, int num_splits) {
+                          float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
+                          __nv_bfloat16* __restrict__ out, int nq, int nkv, int page_size, float scale_log2e, int window,
+                          int split_keys, int num_splits) {
     pdl_trigger();
-    pdl_wait();
+    // The step's index arrays and the keys of earlier steps are not written by the kernels before this one.
     constexpr int ROW_BYTES = HD * 2;
     constexpr int CHUNKS = HD / 8;           // 16-byte chunks per row
     constexpr int KSTEPS = HD / 16;
@@ -44,7 +51,15 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
 
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int seq = seq_of_token[t];
-    if (seq < 0) return;
+    const int group = nq / nkv;
+    if (seq < 0) {        // a padded row: zeros
+        if (split == 0) {
+            pdl_wait();
+            for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
+                out[(static_cast<size_t>(t) * nq + kvh * group) * HD + i] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
     const int pos = positions[t];
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     const int lo = split * split_keys;
@@ -52,7 +67,6 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tg = lane & 3;
-    const int group = nq / nkv;
     const int32_t* table = block_table + static_cast<size_t>(seq) * table_width;
     const int n_tiles = split_keys / kGroupKeys;          // tiles this warp walks: tile j holds keys base(j) .. +15
     auto tile_base = [&](int j) { return lo + j * kGroupKeys + warp * kTileKeys; };
@@ -90,8 +104,16 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
         }
         cp_async_commit();
     };
-    issue(0);
-    issue(1);
+    const bool holds_newest = pos < lo + split_keys;      // the key written by the kernel before this one is in this split
+    if (!holds_newest) {
+        issue(0);
+        issue(1);
+    }
+    pdl_wait();
+    if (holds_newest) {
+        issue(0);
+        issue(1);
+    }
 
     // The query group as the A operand: row r is query head kvh * group + r.
     uint32_t qa[KSTEPS][4];
@@ -228,53 +250,76 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
             part_ml[slot * 2 + 1] = sum;
         }
     }
-}
 
-// out[t, head, :] = sum_s w_s * part_o[s] / sum_s w_s * part_l[s], w_s = 2^(m_s - max m).
-// One block per (head, token): the weights of the splits are computed once, in
-// parallel over the splits, then every thread sums its column with the loads of
-// several splits in flight.
-template <int HD>
-__global__ void __launch_bounds__(HD)
-paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                          __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ seq_of_token,
-                          const int32_t* __restrict__ positions, int nq, int window, int split_keys, int num_splits) {
-    pdl_trigger();
-    pdl_wait();
-    extern __shared__ float weights[];          // num_splits floats, then 32 for the reductions
-    float* scratch = weights + num_splits;
-    const int head = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
-    __nv_bfloat16* dst = out + (static_cast<size_t>(t) * nq + head) * HD;
-    if (seq_of_token[t] < 0) {
-        dst[d] = __float2bfloat16_rn(0.f);
-        return;
+    // ---- the CTA that finishes last for this (token, key head) merges the splits
+    const int s_lo = first / split_keys, n = pos / split_keys - s_lo + 1;      // live splits
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* ticket = tickets + static_cast<size_t>(t) * nkv + kvh;
+        is_last = atomicAdd(ticket, 1) == n - 1;
+        if (is_last) *ticket = 0;       // ready for the next launch; nobody else touches it before then
     }
-    const int pos = positions[t];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = first / split_keys, n = pos / split_keys - s_lo + 1;
-    const size_t base = (static_cast<size_t>(t) * nq + head) * num_splits + s_lo;
-    float mine = -INFINITY;
-    for (int s = d; s < n; s += HD) mine = fmaxf(mine, part_ml[(base + s) * 2]);
-    const float mm = block_max(mine, scratch);
-    float lsum = 0.f;
-    for (int s = d; s < n; s += HD) {
-        const float w = exp2f(part_ml[(base + s) * 2] - mm);
-        weights[s] = w;
-        lsum += w * part_ml[(base + s) * 2 + 1];
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // out[head, :] = sum_s w_s * part_o[s] / sum_s w_s * part_l[s], w_s = 2^(m_s - max m), summed in the order of the
+    // splits whichever CTA happens to do it. A warp per head computes the weights, then a thread per column sums.
+    float* wts = red;                       // [group][n]
+    float* total = red + group * n;         // [group]
+    for (int row = warp; row < group; row += 4) {
+        const size_t base = (static_cast<size_t>(t) * nq + kvh * group + row) * num_splits + s_lo;
+        float mx = -INFINITY;
+        for (int sp = lane; sp < n; sp += 32) {
+            const float v = __ldcg(part_ml + (base + sp) * 2);
+            wts[row * n + sp] = v;
+            mx = fmaxf(mx, v);
+        }
+        mx = warp_max(mx);
+        float lsum = 0.f;
+        for (int sp = lane; sp < n; sp += 32) {
+            const float w = exp2f(wts[row * n + sp] - mx);
+            wts[row * n + sp] = w;
+            lsum += w * __ldcg(part_ml + (base + sp) * 2 + 1);
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) total[row] = lsum;
     }
-    const float total_l = block_sum(lsum, scratch);     // its barriers also publish `weights`
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* col = part_o + base * HD + d;
-    int s = 0;
-    for (; s + 3 < n; s += 4) {
-        float v[4];
+    __syncthreads();
+    // four columns per thread, eight splits in flight
+    for (int idx = threadIdx.x; idx < group * (HD / 4); idx += blockDim.x) {
+        const int row = idx / (HD / 4), d = (idx - row * (HD / 4)) * 4;
+        const size_t base = (static_cast<size_t>(t) * nq + kvh * group + row) * num_splits + s_lo;
+        const float4* col = reinterpret_cast<const float4*>(part_o + base * HD + d);
+        const float* w = wts + row * n;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int sp = 0;
+        for (; sp + 7 < n; sp += 8) {
+            float4 v[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = col[static_cast<size_t>(s + j) * HD];
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(col + static_cast<size_t>(sp + j) * (HD / 4));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = fmaf(weights[s + j], v[j], acc[j]);
+            for (int j = 0; j < 8; ++j) {
+                acc.x = fmaf(w[sp + j], v[j].x, acc.x);
+                acc.y = fmaf(w[sp + j], v[j].y, acc.y);
+                acc.z = fmaf(w[sp + j], v[j].z, acc.z);
+                acc.w = fmaf(w[sp + j], v[j].w, acc.w);
+            }
+        }
+        for (; sp < n; ++sp) {
+            const float4 v = __ldcg(col + static_cast<size_t>(sp) * (HD / 4));
+            acc.x = fmaf(w[sp], v.x, acc.x);
+            acc.y = fmaf(w[sp], v.y, acc.y);
+            acc.z = fmaf(w[sp], v.z, acc.z);
+            acc.w = fmaf(w[sp], v.w, acc.w);
+        }
+        const float inv = 1.f / total[row];
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out + (static_cast<size_t>(t) * nq + kvh * group + row) * HD + d) = packed;
     }
-    for (; s < n; ++s) acc[0] = fmaf(weights[s], col[static_cast<size_t>(s) * HD], acc[0]);
-    dst[d] = __float2bfloat16_rn(((acc[0] + acc[1]) + (acc[2] + acc[3])) / total_l);
 }
 
 // Keys per CTA: a multiple of 64 between 128 and 1024, chosen so that the grid is
@@ -298,22 +343,20 @@ inline int choose_split_keys(int tokens, int nkv, int max_context) {
 template <int HD>
 int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, const __nv_bfloat16* k_pages,
                   const __nv_bfloat16* v_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
-                  const int32_t* positions, float* part_o, float* part_ml, int tokens, int nq, int nkv, int page_size,
-                  float scale, int window, int split_keys, int num_splits, cudaStream_t stream) {
-    const int smem = kStages * 4 * 2 * kTileKeys * HD * 2;
+                  const int32_t* positions, float* part_o, float* part_ml, int* tickets, int tokens, int nq, int nkv,
+                  int page_size, float scale, int window, int split_keys, int num_splits, cudaStream_t stream) {
+    constexpr int smem = kStages * 4 * 2 * kTileKeys * HD * 2;
+    // the merge keeps one weight per (head of the group, split) and one sum per head in the tile ring's memory
+    if (static_cast<long long>(nq / nkv) * (num_splits + 1) * 4 > smem) return STRIDE_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(paged_decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    dim3 grid(num_splits, nkv, tokens);
-    stride::launch(paged_decode_split_kernel<HD>, dim3(grid), dim3(128), smem, stream, q, q_stride, k_pages, v_pages, block_table, table_width,
-                                                               seq_of_token, positions, part_o, part_ml, nq, nkv, page_size,
-                                                               scale * 1.4426950408889634f, window, split_keys, num_splits);
-    const int merge_smem = (num_splits + 32) * static_cast<int>(sizeof(float));
-    stride::launch(paged_decode_merge_kernel<HD>, dim3(dim3(nq, tokens)), dim3(HD), merge_smem, stream, part_o, part_ml, out, seq_of_token, positions,
-                                                                                nq, window, split_keys, num_splits);
+    stride::launch(paged_decode_split_kernel<HD>, dim3(num_splits, nkv, tokens), dim3(128), smem, stream, q, q_stride, k_pages, v_pages,
+                   block_table, table_width, seq_of_token, positions, part_o, part_ml, tickets, out, nq, nkv, page_size,
+                   scale * 1.4426950408889634f, window, split_keys, num_splits);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -328,12 +371,14 @@ long long stride_paged_decode_scratch_floats(int tokens, int nq, int nkv, int hd
     if (tokens <= 0 || nq <= 0 || nkv <= 0 || max_context <= 0) return 0;
     const int split_keys = choose_split_keys(tokens, nkv, max_context);
     const long long splits = (max_context + split_keys - 1) / split_keys;
-    return static_cast<long long>(tokens) * nq * splits * (hd + 2);
+    return kTicketInts + static_cast<long long>(tokens) * nq * splits * (hd + 2);
 }
 
-// One query token per entry of the flat batch (decode). Returns -2 for sizes it
-// does not run (head sizes other than 64 and 128, groups above 16, more than
-// 65535 tokens); the caller then uses the generic kernel.
+// One query token per entry of the flat batch (decode). `scratch` must be zero when it is
+// first used (the ticket counters at its start; every launch leaves them zero again) and
+// belongs to one stream at a time. Returns -2 for sizes it does not run (head sizes other
+// than 64 and 128, groups above 16, more than 65535 tokens, more than 65536 (token, key head)
+// pairs); the caller then uses the generic kernel.
 int stride_paged_decode_attention(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                   const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                                   const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,
@@ -346,20 +391,22 @@ int stride_paged_decode_attention(const void* q, int q_stride, void* out, const 
     if (tokens == 0) return 0;
     const int split_keys = choose_split_keys(tokens, nkv, max_context);
     const int num_splits = (max_context + split_keys - 1) / split_keys;
-    if (num_splits > 8192) return STRIDE_UNSUPPORTED;
+    if (num_splits > 8192 || static_cast<long long>(tokens) * nkv > kTicketInts) return STRIDE_UNSUPPORTED;
     const long long need = stride_paged_decode_scratch_floats(tokens, nq, nkv, hd, max_context);
     if (scratch == nullptr || scratch_floats < need) return STRIDE_BAD_ARGUMENT;
-    float* part_o = scratch;
-    float* part_ml = scratch + static_cast<long long>(tokens) * nq * num_splits * hd;
+    static_assert(sizeof(int) == sizeof(float), "the tickets live in the float scratch");
+    int* tickets = reinterpret_cast<int*>(scratch);
+    float* part_o = scratch + kTicketInts;
+    float* part_ml = part_o + static_cast<long long>(tokens) * nq * num_splits * hd;
     auto qp = static_cast<const __nv_bfloat16*>(q);
     auto op = static_cast<__nv_bfloat16*>(out);
     auto kp = static_cast<const __nv_bfloat16*>(k_pages);
     auto vp = static_cast<const __nv_bfloat16*>(v_pages);
     if (hd == 64)
         return launch_decode<64>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
-                                 tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
+                                 tickets, tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
     return launch_decode<128>(qp, q_stride, op, kp, vp, block_table, table_width, seq_of_token, positions, part_o, part_ml,
-                              tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
+                              tickets, tokens, nq, nkv, page_size, scale, window, split_keys, num_splits, stream);
 }
 
 }  // extern "C"

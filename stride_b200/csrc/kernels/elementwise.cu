@@ -192,8 +192,15 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int32_t* __restrict__ rows, int hidden, float eps) {
     pdl_trigger();
-    pdl_wait();
     __shared__ float scratch[32];
+    // the norm's weight does not depend on the kernel before this one: fetch it while that one finishes
+    float4 wv[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (it * blockDim.x + threadIdx.x) * 4;
+        wv[it] = c < hidden ? *reinterpret_cast<const float4*>(weight + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
     const int r = blockIdx.x;
     const size_t s = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
     float* res = residual + s * hidden;
@@ -235,7 +242,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     for (int it = 0; it < ITERS; ++it) {
         const int c = (it * blockDim.x + threadIdx.x) * 4;
         if (c < hidden) {
-            const float4 w = *reinterpret_cast<const float4*>(weight + c);
+            const float4 w = wv[it];
             const float y0 = __fmul_rn(__fmul_rn(x[it].x, inv), w.x), y1 = __fmul_rn(__fmul_rn(x[it].y, inv), w.y);
             const float y2 = __fmul_rn(__fmul_rn(x[it].z, inv), w.z), y3 = __fmul_rn(__fmul_rn(x[it].w, inv), w.w);
             if constexpr (sizeof(T) == 2) {

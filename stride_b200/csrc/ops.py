@@ -313,7 +313,8 @@ def decode_scratch_floats(tokens: int, nq: int, nkv: int, hd: int, max_context: 
 def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table, seq_of_token, positions, scratch, nq: int,
                            nkv: int, hd: int, page_size: int, scale: float, window: int, max_context: int) -> None:
     """Attention for single decoded tokens (one query per row), split over the keys;
-    ``scratch`` (float32) holds the partial results of the splits."""
+    ``scratch`` (float32, zero when first used) holds the ticket counters and the
+    partial results of the splits."""
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
@@ -323,7 +324,6 @@ def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table,
         _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
         int(max_context), _stream()), "paged_attention_decode")
-    counters["launches"] += 1       # the launcher runs two kernels
 
 
 TC_ATTENTION = _os.environ.get("STRIDE_B200_TC_ATTENTION", "1") != "0"

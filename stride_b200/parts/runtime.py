@@ -41,13 +41,15 @@ class Runtime:
         """A flat scratch buffer of at least ``numel`` elements. It only ever grows,
         and growing happens outside graph capture (the warm-up run of a bucket
         asks for the same size as the captured run); a buffer that was outgrown
-        stays allocated, because an earlier graph may hold its address."""
+        stays allocated, because an earlier graph may hold its address. New buffers
+        are zeroed: kernels that count themselves off on tickets keep those in
+        their scratch, zero between launches."""
         key = ("scratch", tag, dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < numel:
             if buf is not None:
                 self._retired.append(buf)      # a captured graph may still write to it: never hand it back
-            buf = torch.empty(int(numel), dtype=dtype, device=self.device)
+            buf = torch.zeros(int(numel), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf
 

@@ -348,12 +348,16 @@ def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
     seq_of = torch.cat([seq_of, torch.tensor([-1], dtype=torch.int32)])
     pos = torch.cat([pos, torch.zeros(1, dtype=torch.int32)])
     for bound in (1501, 4096, 200000):
-        out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+        # the scratch starts with the ticket counters (zero before the first launch); what follows is poisoned
         scratch = torch.full((ops.decode_scratch_floats(q.shape[0], nq, nkv, hd, bound),), float("nan"), device="cuda")
-        ops.paged_attention_decode(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), scratch,
-                                   nq, nkv, hd, page, hd ** -0.5, window or 0, bound)
-        close(out[:-1], want, dtype)
-        assert float(out[-1].abs().max()) == 0.0
+        scratch[:65536] = 0
+        for _ in range(2):      # twice on the same scratch: the tickets must be ready again
+            out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+            ops.paged_attention_decode(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), scratch,
+                                       nq, nkv, hd, page, hd ** -0.5, window or 0, bound)
+            close(out[:-1], want, dtype)
+            assert float(out[-1].abs().max()) == 0.0
+        assert int(scratch[:65536].view(torch.int32).abs().max()) == 0, "a launch left a ticket behind"
     assert ops.fast_attention_supported(dtype, nq, nkv, hd)
     assert not ops.fast_attention_supported(dtype, 34, 2, 128) and not ops.fast_attention_supported(dtype, 4, 2, 48)
     assert not ops.fast_attention_supported(torch.float32, 4, 2, 128)

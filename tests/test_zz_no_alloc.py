@@ -61,7 +61,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         tokens = q.shape[0]
         assert 0 < floats(tokens, nq, nkv, hd, bound) <= CAPACITY
         want = torch.full((tokens, nq * hd), 3.0, dtype=torch.bfloat16, device="cuda")
-        scratch = torch.empty(ops.decode_scratch_floats(tokens, nq, nkv, hd, bound), device="cuda")
+        scratch = torch.zeros(ops.decode_scratch_floats(tokens, nq, nkv, hd, bound), device="cuda")
         ops.paged_attention_decode(q, nq * hd, want, k_pages, v_pages, table, seq_of, positions, scratch, nq, nkv, hd, page,
                                    hd ** -0.5, 0, bound)
         got = torch.full_like(want, 5.0)
