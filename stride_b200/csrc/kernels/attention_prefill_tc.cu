@@ -11,35 +11,41 @@
 // There are two score buffers in tensor memory and the scores run two tiles ahead: S of tile
 // j+2 is issued right after the output product of tile j, so the softmax warps go from one
 // tile to the next without waiting for the tensor cores, and the products hide behind them.
-// Q, K and V arrive by TMA: Q as a 128-row box of the projection output, K and V page by page
-// through the request's block table (a page's keys of one head are contiguous in the cache, so
-// a page is one box per 64 columns). The output accumulator is rescaled only when a row's
-// maximum has grown by more than 2^8 since the value in use, which keeps tensor-memory traffic
-// low and the exponentials bounded. The mask is that of python/stride_worker/layers.py:109-149
-// (key <= query position) plus an optional window.
 //
-// Roles: warp 0 issues TMA, warp 1 issues the products and owns tensor memory, warps 2-5 do the
-// softmax and the final store. Every mbarrier wait is bounded; a wait that runs out sets *status.
+// Q arrives by TMA as one 128-row box of the projection output. Keys and values come through
+// the request's block table with cp.async, 16 bytes per thread, written in the 128-byte-swizzle
+// layout the products expect: a page is small (16 keys of one head are 4 KB) and a TMA copy per
+// page and 64-column half cost more to issue than the softmax of the tile takes (measured: 16
+// copies of 2 KB per tile held the tile at 3300 cycles, the softmax needs 1400), while
+// one warp per stream with cp.async keeps up for any page size. The output accumulator is
+// rescaled only when a row's maximum has grown by more than 2^8 since the value in use, which
+// keeps tensor-memory traffic low and the exponentials bounded. The mask is that of
+// python/stride_worker/layers.py:109-149 (key <= query position) plus an optional window.
+//
+// Roles: warp 0 copies keys, warp 1 issues the products and owns tensor memory, warp 2 copies
+// values, warp 3 fetches Q, warps 4-7 do the softmax and the final store. Every mbarrier wait
+// is bounded; a wait that runs out sets *status.
 #include "tcgen05.cuh"
+#include "mma.cuh"
 
 namespace stride {
 namespace tc {
 
 constexpr int kQRows = 128;
 constexpr int kKeys = 64;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 256;
 constexpr float kRescaleThreshold = 8.f;      // in log2 units
 
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, 2)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfloat16* __restrict__ k_pages,
+                       const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
                        const int32_t* __restrict__ q_len, const int32_t* __restrict__ ctx_len, int num_seqs, int nq, int nkv,
-                       int page_size, float scale_log2e, int window, int* __restrict__ status) {
+                       int page_shift, float scale_log2e, int window, int* __restrict__ status) {
     constexpr int HALVES = HD / 64;                       // 64-column boxes per row
     constexpr int HALF_BYTES = kQRows * 128;              // a [128 rows x 64 columns] bf16 box of Q
-    constexpr int KV_HALF_BYTES = kKeys * 128;            // a [64 keys x 64 columns] box of K or V
+    constexpr int KV_HALF_BYTES = kKeys * 128;            // [64 keys x 64 columns] of K or V
     constexpr int Q_BYTES = HALVES * HALF_BYTES;
     constexpr int KV_BYTES = HALVES * KV_HALF_BYTES;      // one K tile or one V tile
     constexpr uint32_t TMEM_COLS = 256;                   // two score buffers (P over S) of 64 columns, O: HD columns
@@ -88,9 +94,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&p_full[s]), 4);
-            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&k_full[s]), 32);       // one arrival per lane of the copying warp
             mbar_init(smem_u32(&k_empty[s]), 1);
-            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 32);
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -102,41 +108,55 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 2 * kKeys;     // score buffer b at tmem_s + b * kKeys
     pdl_wait();       // queries, keys and values were written by the kernels before this one
 
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer. Keys of tile j go to k_s[j & 1] once the scores of tile j-2 are done, values of
-            // tile j to v_s[j & 1] once the output product of tile j-2 is done; keys run two tiles ahead.
+    if (warp == 0 || warp == 2) {
+        // ---- copying warps: warp 0 walks the key tiles, warp 2 the value tiles. A lane owns one 16-byte
+        // chunk position of the row (cc) and every (32 / chunks per row)-th key; the block table is read
+        // 32 pages at a time, one entry per lane, and handed round by shuffle.
+        const bool is_k = warp == 0;
+        const __nv_bfloat16* pages = is_k ? k_pages : v_pages;
+        unsigned char* ring = is_k ? k_s : v_s;
+        uint64_t* full = is_k ? k_full : v_full;
+        uint64_t* empty = is_k ? k_empty : v_empty;
+        constexpr int CPR = HD / 8;                         // 16-byte chunks per row
+        constexpr int RPI = 32 / CPR;                       // rows per iteration of the warp
+        const int cc = lane % CPR, sub = lane / CPR;
+        const int page_size = 1 << page_shift;
+        const int first_page = (kt_first * kKeys) >> page_shift;
+        const uint32_t dst_lane = static_cast<uint32_t>((cc >> 3) * KV_HALF_BYTES);
+        int win_at = -1, win_entry = 0;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            if (!mbar_wait(smem_u32(&empty[st]), (static_cast<uint32_t>(j >> 1) & 1u) ^ 1u, status, is_k ? 11 : 18)) break;
+            const int k0 = (kt_first + j) * kKeys;
+            {   // a tile never straddles a window of 32 pages (tiles and windows are aligned)
+                const int at = ((k0 >> page_shift) - first_page) >> 5;
+                if (at != win_at) {
+                    const int idx = first_page + at * 32 + lane;
+                    win_entry = idx < table_width ? table[idx] : 0;
+                    win_at = at;
+                }
+            }
+            unsigned char* dst_tile = ring + st * KV_BYTES + dst_lane;
+#pragma unroll 4
+            for (int it = 0; it < kKeys / RPI; ++it) {
+                const int r = it * RPI + sub;
+                const int key = k0 + r;
+                const bool valid = key >= first_key && key <= last_pos;      // other rows keep what they held: masked (K) or cleared (V) later
+                const int page_rel = (min(key, last_pos) >> page_shift) - first_page;
+                const int entry = __shfl_sync(0xffffffffu, win_entry, page_rel & 31);
+                if (valid) {
+                    const size_t src_row = (static_cast<size_t>(entry) * nkv + kvh) * page_size + (key & (page_size - 1));
+                    cp_async_16(dst_tile + r * 128 + (((cc & 7) ^ (r & 7)) << 4), pages + src_row * HD + cc * 8);
+                }
+            }
+            cp_async_arrive_noinc(smem_u32(&full[st]));
+        }
+        cp_async_wait<0>();
+    } else if (warp == 3) {
+        if (lane == 0) {       // ---- Q: one box per 64 columns
             const uint32_t qb = smem_u32(&q_full);
             mbar_expect_tx(qb, Q_BYTES);
             for (int h = 0; h < HALVES; ++h) tma_load_2d(smem_u32(q_s + h * HALF_BYTES), &map_q, qb, head * HD + h * 64, q_row0);
-            const int pages_per_tile = kKeys / page_size;
-            const uint32_t page_bytes = static_cast<uint32_t>(page_size) * 128;       // one page, one 64-column box
-            auto load_tile = [&](const CUtensorMap* map, unsigned char* ring, uint64_t* full, uint64_t* empty, int j, int code) {
-                const int st = j & 1;
-                if (!mbar_wait(smem_u32(&empty[st]), (static_cast<uint32_t>(j >> 1) & 1u) ^ 1u, status, code)) return false;
-                const int k0 = (kt_first + j) * kKeys;
-                int needed = 0;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    const int lo = k0 + i * page_size;
-                    needed += (lo <= last_pos && lo + page_size > first_key);
-                }
-                const uint32_t bar = smem_u32(&full[st]);
-                mbar_expect_tx(bar, static_cast<uint32_t>(needed) * HALVES * page_bytes);
-                unsigned char* dst = ring + st * KV_BYTES;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    const int lo = k0 + i * page_size;
-                    if (!(lo <= last_pos && lo + page_size > first_key)) continue;
-                    const int y = (table[lo / page_size] * nkv + kvh) * page_size;
-                    for (int h = 0; h < HALVES; ++h) tma_load_2d(smem_u32(dst + h * KV_HALF_BYTES) + i * page_bytes, map, bar, h * 64, y);
-                }
-                return true;
-            };
-            bool ok = load_tile(&map_k, k_s, k_full, k_empty, 0, 11);
-            if (ok && n_tiles > 1) ok = load_tile(&map_k, k_s, k_full, k_empty, 1, 11);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = load_tile(&map_v, v_s, v_full, v_empty, j, 18);
-                if (ok && j + 2 < n_tiles) ok = load_tile(&map_k, k_s, k_full, k_empty, j + 2, 11);
-            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -147,6 +167,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             auto scores = [&](int j) {
                 const int st = j & 1;
                 if (!mbar_wait(smem_u32(&k_full[st]), static_cast<uint32_t>(j >> 1) & 1u, status, 13)) return false;
+                fence_proxy_async();         // the keys were written by cp.async, the product reads them through the async proxy
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(k_s + st * KV_BYTES);
 #pragma unroll
@@ -164,8 +185,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j & 1;
                 const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
-                ok = mbar_wait(smem_u32(&v_full[st]), ph, status, 19) && mbar_wait(smem_u32(&p_full[st]), ph, status, 14);
+                ok = mbar_wait(smem_u32(&v_full[st]), ph, status, 19);
+                ok = ok && mbar_wait(smem_u32(&p_full[st]), ph, status, 14);
                 if (!ok) break;
+                fence_proxy_async();
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(v_s + st * KV_BYTES);
 #pragma unroll
@@ -181,7 +204,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
         }
     } else {
-        // ---- softmax and output: warps 2..5 own tensor-memory lanes 64-95, 96-127, 0-31, 32-63
+        // ---- softmax and output: warps 4..7 own tensor-memory lanes 0-31, 32-63, 64-95, 96-127
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                    // query row of the tile, also the key row this thread may clear
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -197,22 +220,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) break;
             tc_fence_after();
             const bool edge = k0 + kKeys - 1 > pos0 || (window > 0 && k0 <= last_pos - window);   // some (row, key) is masked
-            float sv[kKeys];                                 // raw scores; a masked one is -inf
-            float mx = -INFINITY;
-            tmem_ld64(tmem_sj, sv);
-            if (edge) {
+            // The 64 scores are taken in two halves of 32 to stay within the registers that two CTAs per SM leave:
+            // first the maximum over both (the second half stays in registers), then P for the second half, then
+            // the first half again from tensor memory.
+            float sv[32];                                    // raw scores of one half; a masked one is -inf
+            auto load_half = [&](int half) {
+                tmem_ld32(tmem_sj + half * 32, sv);
+                if (edge) {
 #pragma unroll
-                for (int i = 0; i < kKeys; ++i) {
-                    const int key = k0 + i;
-                    if (!(key <= pos_r && (window <= 0 || key > pos_r - window))) sv[i] = -INFINITY;
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = k0 + half * 32 + i;
+                        if (!(key <= pos_r && (window <= 0 || key > pos_r - window))) sv[i] = -INFINITY;
+                    }
                 }
-            }
+            };
+            auto half_max = [&]() {       // four independent chains of three-input maxima
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < kKeys; ++i) mx = fmaxf(mx, sv[i]);
-            mx *= scale_log2e;                               // the scale is positive: the maximum of the scaled scores
+                for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) m4[c] = max3(m4[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
+                }
+                return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            };
+            load_half(0);
+            float mx = half_max();
+            load_half(1);
+            mx = fmaxf(mx, half_max()) * scale_log2e;        // the scale is positive: the maximum of the scaled scores
             const bool grow = mx > m_ref + kRescaleThreshold;      // also true for the first finite maximum
             // Every warp waits for every phase of pv_done exactly once (a parity wait cannot skip a phase):
-            // before a rescale if there is one, else at the end of the iteration, where it costs nothing.
+            // before a rescale if there is one, else at the end of the iteration, by when it has long completed.
             bool waited = j == 0;
             if (__any_sync(0xffffffffu, grow)) {
                 const float factor = grow ? (m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - mx)) : 1.f;
@@ -238,16 +275,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // A masked score is -inf and gives exactly 0. A row that has seen no key yet has m_ref = -inf and
                 // only masked scores: subtract 0 there, or -inf - -inf would make a NaN.
                 const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-                float packed[kKeys / 2];       // bfloat16 pairs, carried as 32-bit words
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};       // independent partial sums
+                float packed[32];             // bfloat16 pairs, carried as 32-bit words: P's columns hold two keys each
+                auto pack_half = [&](int half) {
 #pragma unroll
-                for (int i = 0; i < kKeys; i += 2) {
-                    const float p0 = ex2_approx(fmaf(sv[i], scale_log2e, neg_m));
-                    const float p1 = ex2_approx(fmaf(sv[i + 1], scale_log2e, neg_m));
-                    l += p0 + p1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                    packed[i / 2] = __uint_as_float(*reinterpret_cast<uint32_t*>(&b));
-                }
-                tmem_st32(tmem_sj, packed);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2_approx(fmaf(sv[i], scale_log2e, neg_m));
+                        const float p1 = ex2_approx(fmaf(sv[i + 1], scale_log2e, neg_m));
+                        l4[(i / 2) & 3] += p0 + p1;
+                        packed[half * 16 + i / 2] = __uint_as_float(pack_bf16(p0, p1));
+                    }
+                };
+                pack_half(1);                 // the second half is still in registers
+                load_half(0);
+                pack_half(0);
+                tmem_st32(tmem_sj, packed);   // over S columns 0-31, all of which have been read
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             }
             // Key rows that no query of this tile may see can hold anything (a page never written, the
             // rest of a page): clear their values, or 0 * garbage would poison the product.
@@ -265,10 +308,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 fence_proxy_async();
             }
+            // Before this warp lets the output product of tile j go: once that one can finish, pv_done may be
+            // two phases on and its parity says nothing any more.
+            if (!waited) ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(j - 1) & 1u, status, 21);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[st]));
-            if (!waited) ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(j - 1) & 1u, status, 21);
         }
         if (ok) ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(n_tiles - 1) & 1u, status, 17);
         tc_fence_after();
@@ -285,10 +330,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 b = __floats2bfloat162_rn(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
-                            w[e] = *reinterpret_cast<uint32_t*>(&b);
-                        }
+                        for (int e = 0; e < 4; ++e) w[e] = pack_bf16(v[q4 * 8 + 2 * e] * inv, v[q4 * 8 + 2 * e + 1] * inv);
                         *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
@@ -301,9 +343,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 template <int HD>
-int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtensorMap* map_v, __nv_bfloat16* out,
+int launch_attn(const CUtensorMap* map_q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out,
                 const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
-                int num_seqs, int max_tiles, int nq, int nkv, int page_size, float scale, int window, int* status,
+                int num_seqs, int max_tiles, int nq, int nkv, int page_shift, float scale, int window, int* status,
                 cudaStream_t stream) {
     constexpr int smem = (HD / 64) * (kQRows * 128 + 4 * kKeys * 128) + 1024;      // Q, two key tiles, two value tiles
     static bool configured = false;
@@ -313,8 +355,8 @@ int launch_attn(const CUtensorMap* map_q, const CUtensorMap* map_k, const CUtens
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(max_tiles, nq), dim3(kAttnThreads), smem, stream, *map_q, *map_k, *map_v, out, block_table,
-                   table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_size, scale * 1.4426950408889634f, window, status);
+    stride::launch(kernel, dim3(max_tiles, nq), dim3(kAttnThreads), smem, stream, *map_q, k_pages, v_pages, out, block_table,
+                   table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift, scale * 1.4426950408889634f, window, status);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -326,7 +368,7 @@ using namespace stride;
 // Attention for the first `num_seqs` requests of the step, which own the first `tokens` rows of
 // the flat batch. q: [tokens, q_stride] bf16 (head h at columns h*hd); out: [tokens, nq*hd];
 // pages: [num_pages, nkv, page_size, hd]. Returns -2 for what it does not take (head sizes other
-// than 64 and 128, page sizes that are not 8, 16, 32 or 64, unaligned strides); the caller
+// than 64 and 128, page sizes that are no power of two from 4 to 64, unaligned strides); the caller
 // then uses the mma.sync kernel.
 extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                                  int num_pages, const int32_t* block_table, int table_width,
@@ -336,21 +378,23 @@ extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, vo
     if (tokens < 0 || num_seqs < 0 || nq <= 0 || nkv <= 0 || page_size <= 0 || table_width <= 0 || window < 0 || num_pages <= 0)
         return STRIDE_BAD_ARGUMENT;
     if (nq % nkv || status == nullptr) return STRIDE_BAD_ARGUMENT;
-    if ((hd != 64 && hd != 128) || page_size % 8 || tc::kKeys % page_size || q_stride % 8 || nq > 65535) return STRIDE_UNSUPPORTED;
+    if ((hd != 64 && hd != 128) || page_size > tc::kKeys || page_size < 4 || q_stride % 8 || nq > 65535) return STRIDE_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(k_pages) |
          reinterpret_cast<uintptr_t>(v_pages)) % 16)
         return STRIDE_UNSUPPORTED;
     if (tokens == 0 || num_seqs == 0) return 0;
-    const long long cache_rows = static_cast<long long>(num_pages) * nkv * page_size;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    if ((1 << page_shift) != page_size) return STRIDE_UNSUPPORTED;
     const CUtensorMap* map_q = tc::cached_map(q, tokens, q_stride, q_stride, tc::kQRows);
-    const CUtensorMap* map_k = tc::cached_map(k_pages, cache_rows, hd, hd, page_size);
-    const CUtensorMap* map_v = tc::cached_map(v_pages, cache_rows, hd, hd, page_size);
-    if (!map_q || !map_k || !map_v) return STRIDE_UNSUPPORTED;
+    if (!map_q) return STRIDE_UNSUPPORTED;
     const int max_tiles = (tokens + tc::kQRows - 1) / tc::kQRows + num_seqs;
     auto op = static_cast<__nv_bfloat16*>(out);
+    auto kp = static_cast<const __nv_bfloat16*>(k_pages);
+    auto vp = static_cast<const __nv_bfloat16*>(v_pages);
     if (hd == 64)
-        return tc::launch_attn<64>(map_q, map_k, map_v, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles,
-                                   nq, nkv, page_size, scale, window, status, stream);
-    return tc::launch_attn<128>(map_q, map_k, map_v, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq,
-                                nkv, page_size, scale, window, status, stream);
+        return tc::launch_attn<64>(map_q, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq,
+                                   nkv, page_shift, scale, window, status, stream);
+    return tc::launch_attn<128>(map_q, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq, nkv,
+                                page_shift, scale, window, status, stream);
 }

@@ -181,7 +181,7 @@ def _tc_buffers(device, partial_floats: int):
     st = _tc_state.get(device)
     if st is None:
         st = {"tickets": torch.zeros(_TC_TICKETS, dtype=torch.int32, device=device),
-              "status": torch.zeros(1, dtype=torch.int32, device=device), "partials": None, "retired": []}
+              "status": torch.zeros(64, dtype=torch.int32, device=device), "partials": None, "retired": []}
         _tc_state[device] = st
     if partial_floats and (st["partials"] is None or st["partials"].numel() < partial_floats):
         if st["partials"] is not None:
@@ -203,8 +203,24 @@ def _tc_scratch_floats(n_out: int, tokens: int, k: int) -> int:
 def tc_status(device=None) -> int:
     """0, or the code of the first bounded wait that ran out inside the tcgen05
     kernels (1 producer, 2 tensor-core issuer, 3 epilogue). Synchronises."""
-    codes = [int(st["status"].item()) for dev, st in _tc_state.items() if device is None or dev == device]
+    codes = [int(st["status"][0].item()) for dev, st in _tc_state.items() if device is None or dev == device]
     return next((c for c in codes if c), 0)
+
+
+_WAIT_CODES = {1: "matrix product: producer", 2: "matrix product: tensor-core issuer", 3: "matrix product: epilogue"}
+
+
+def raise_on_kernel_status(code: int) -> None:
+    """Raises when ``code`` (the status word, read back by the caller) is not 0: a bounded wait inside a
+    tcgen05 kernel ran out, so what that kernel wrote is not to be trusted."""
+    if code:
+        raise KernelError(f"a bounded wait inside a tcgen05 kernel ran out (code {code}: "
+                          f"{_WAIT_CODES.get(code, 'attention, see attention_prefill_tc.cu')}); the step's results are invalid")
+
+
+def check_kernel_status(device=None) -> None:
+    """Reads the status word (synchronises) and raises if a kernel recorded a timed-out wait."""
+    raise_on_kernel_status(tc_status(device))
 
 
 def status_tensor(device):

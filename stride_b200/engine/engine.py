@@ -101,6 +101,7 @@ class Engine:
         self._sample_dev = torch.zeros(3 * row_cap, dtype=torch.float32, device=self.model.rt.device)
         self._tokens_dev = torch.zeros(row_cap, dtype=torch.int32, device=self.model.rt.device)
         self._tokens_host = torch.zeros(row_cap, dtype=torch.int32, pin_memory=pin)
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)     # the kernels' timed-out-wait word, read back with the tokens
         self._row_cap = row_cap
         self.forward_passes = 0
         self.busy_us = 0
@@ -233,9 +234,11 @@ class Engine:
         ops.sample_rows(logits, self._tokens_dev[:n], temperature=dev[:n], uniform=dev[cap:cap + n],
                         suppress=dev[2 * cap:2 * cap + n].view(torch.int32))
         self._tokens_host[:n].copy_(self._tokens_dev[:n], non_blocking=True)
+        self._status_host.copy_(ops.status_tensor(self._tokens_dev.device)[:1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        ops.raise_on_kernel_status(int(self._status_host[0]))
         self.h2d_bytes += self._sample_host.numel() * 4
-        self.d2h_bytes += n * 4
+        self.d2h_bytes += n * 4 + 4
         tokens = self._tokens_host[:n].tolist()
         if ranked_rows:
             rows = logits[torch.as_tensor(ranked_rows, device=logits.device)].cpu().numpy()

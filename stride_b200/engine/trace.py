@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
 from ..csrc.build import load_runtime
 from .loading import CachePlan, attach_cache, load_model
 from .runner import ModelRunner
@@ -81,6 +82,7 @@ class TraceSession:
         logits = None
         if batch.num_tokens:
             out = self.runner.step(batch, to_host=True)
+            ops.check_kernel_status()
             logits = out if batch.num_rows else None
             for e in entries:
                 rid = str(e["id"])

@@ -498,6 +498,24 @@ def test_prefill_attention_on_tcgen05(ops, nq, nkv, hd, page, window):
     close(out, mma.float(), dtype)
 
 
+def test_prefill_attention_on_tcgen05_walks_long_contexts(ops):
+    """Portions deep inside long contexts: a hundred and more key tiles per query tile, so every ring and
+    barrier of the kernel wraps many times; none of its bounded waits may run out."""
+    g = torch.Generator().manual_seed(24)
+    dtype = torch.bfloat16
+    nq, nkv, hd, page = 8, 2, 128, 16
+    seqs = [(6100, 1024), (3333, 515), (0, 700)]
+    q, k_pages, v_pages, table, _seq_of, _pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, None, spike=(None, 2))
+    q_start, q_len, ctx_len = _seq_arrays(seqs)
+    for _ in range(3):
+        out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+        assert ops.paged_attention_prefill_tc(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                              dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, 0)
+        torch.cuda.synchronize()
+        assert ops.tc_status() == 0
+        close(out, want, dtype)
+
+
 def test_prefill_attention_on_tcgen05_refuses_odd_page_sizes(ops):
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     q = torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda")
