@@ -322,11 +322,13 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, con
     }
 }
 
-// Keys per CTA: a multiple of 64 between 128 and 1024, chosen so that the grid is
-// two to three waves of resident CTAs (measured on a B200 at 8k context: every
-// CTA pays a fixed start-up of dependent loads, so fewer, longer CTAs win as long
-// as the SMs stay filled). It depends only on the launch's sizes (not on the
-// contexts of the moment), so a captured graph stays valid.
+// Keys per CTA: a multiple of 64 between 128 and 1024. Measured on a B200 (8 key heads, context 8192, inside
+// the captured decode step): every CTA pays a fixed start-up of dependent loads, so fewer, longer CTAs win as
+// long as the SMs stay filled, and a last wave that is nearly full beats one more wave. With enough work the
+// grid is therefore sized to about 1.85 waves of the 444 CTAs that fit (batch 8: 640 keys, 832 CTAs, 3 us a
+// layer faster than 448 keys); with little work to about 1.4 CTAs per SM (batch 1: 320 keys instead of 128,
+// 4 us a layer). The choice depends only on the launch's sizes (not on the contexts of the moment), so a
+// captured graph stays valid.
 inline int choose_split_keys(int tokens, int nkv, int max_context) {
     static const int forced = [] {      // tuning hook: STRIDE_DECODE_SPLIT_KEYS=<multiple of 64>
         const char* e = getenv("STRIDE_DECODE_SPLIT_KEYS");
@@ -335,7 +337,8 @@ inline int choose_split_keys(int tokens, int nkv, int max_context) {
     }();
     if (forced) return forced;
     const long long groups = static_cast<long long>(tokens) * nkv * ((max_context + kGroupKeys - 1) / kGroupKeys);
-    long long u = groups / 1100;
+    long long u = (groups + 820) / 821;                 // 1.85 waves of 148 SMs x 3 CTAs
+    if (u < 4) u = (groups + 206) / 207;                // too little work for that: 1.4 CTAs per SM
     u = u < 2 ? 2 : (u > 16 ? 16 : u);
     return static_cast<int>(u) * kGroupKeys;
 }
