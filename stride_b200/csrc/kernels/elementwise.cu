@@ -131,18 +131,20 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// in is [tokens, 2 * inter] (gate columns, then up columns); out is [tokens, inter].
-// silu(z) = z * sigmoid(z) (python/stride_worker/layers.py:161), in float32.
+// in is [tokens, 2 * inter], out is [tokens, inter]. The gate and up columns alternate in blocks of `block`
+// columns (gate 0..block-1, up 0..block-1, gate block.., ...); block == inter is the plain layout, all gate
+// columns and then all up columns. silu(z) = z * sigmoid(z) (python/stride_worker/layers.py:161), in float32.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, size_t total) {
     pdl_trigger();
     pdl_wait();
     size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
     const int i = static_cast<int>(idx - t * inter);
-    const float g = to_f32(in[t * 2 * inter + i]);
-    const float u = to_f32(in[t * 2 * inter + inter + i]);
+    const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
+    const float g = to_f32(in[at]);
+    const float u = to_f32(in[at + block]);
     const float silu = g / (1.f + expf(-g));
     out[idx] = from_f32<T>(silu * u);
 }
@@ -316,9 +318,9 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
     }
 }
 
-// silu_mul_kernel with 16-byte accesses (inter % V == 0).
+// silu_mul_kernel with 16-byte accesses (block % V == 0).
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, size_t packs) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, size_t packs) {
     pdl_trigger();
     pdl_wait();
     constexpr int V = Pack<T>::V;
@@ -328,8 +330,9 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ ou
         const size_t t = idx / per_row;
         const int i = static_cast<int>(idx - t * per_row) * V;
         Pack<T> g, u;
-        g.load(in + t * 2 * inter + i);
-        u.load(in + t * 2 * inter + inter + i);
+        const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
+        g.load(in + at);
+        u.load(in + at + block);
 #pragma unroll
         for (int j = 0; j < V; ++j) g.v[j] = (g.v[j] / (1.f + expf(-g.v[j]))) * u.v[j];
         g.store(out + t * inter + i);
@@ -474,28 +477,28 @@ int stride_rope_kv_write(void* qkv, const float* bias, const int32_t* positions,
     return STRIDE_LAUNCH_STATUS();
 }
 
-int stride_silu_mul(const void* in, void* out, int tokens, int inter, int dtype, cudaStream_t stream) {
-    if (tokens < 0 || inter <= 0) return STRIDE_BAD_ARGUMENT;
+int stride_silu_mul(const void* in, void* out, int tokens, int inter, int block, int dtype, cudaStream_t stream) {
+    if (tokens < 0 || inter <= 0 || block <= 0 || inter % block) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     const size_t total = static_cast<size_t>(tokens) * inter;
     const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
     {
         const uintptr_t bits = reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out);
         const int vec = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
-        if (bits % 16 == 0 && inter % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
+        if (bits % 16 == 0 && block % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
             const size_t packs = total / vec;
             const unsigned vblocks = static_cast<unsigned>(std::min<size_t>((packs + 255) / 256, 148 * 16));
             if (dtype == STRIDE_DTYPE_F32)
-                stride::launch(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, packs);
+                stride::launch(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, block, packs);
             else
-                stride::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, packs);
+                stride::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, block, packs);
             return STRIDE_LAUNCH_STATUS();
         }
     }
     if (dtype == STRIDE_DTYPE_F32)
-        stride::launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, total);
+        stride::launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, block, total);
     else if (dtype == STRIDE_DTYPE_BF16)
-        stride::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, total);
+        stride::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, block, total);
     else
         return STRIDE_BAD_ARGUMENT;
     return STRIDE_LAUNCH_STATUS();

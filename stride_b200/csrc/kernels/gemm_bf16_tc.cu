@@ -45,7 +45,10 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
 
 // D tile rows are rows of A, columns are rows of B. TRANSPOSED: out[col * ldo + row]
 // (swapped use: rows are output features, columns tokens); else out[row * ldo + col].
-template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename OutT>
+// GATED (swapped use, one split, bfloat16 out): the rows of A alternate in blocks of 64 between the gate and the
+// up matrix of a gated feed-forward; the tile's rows 0-63 and 64-127 then belong together, and the epilogue writes
+// silu(gate) * up, 64 columns of the inner activation per tile, instead of the 128 products.
+template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename OutT, bool GATED = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out,
                     int ldo, int M, int N, int K, int k_blocks_per_split, float* __restrict__ partials,
@@ -140,7 +143,37 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         float* my_partial = split ? partials + ((static_cast<size_t>(blockIdx.z) * gridDim.x * gridDim.y + tile) * kBlockM + row) * BLOCK_N
                                   : nullptr;
-        if (ok) {
+        if constexpr (GATED) {
+            static_assert(!GATED || (BLOCK_N == 16 && TRANSPOSED), "the gated epilogue is written for one 16-token column block");
+            float v[16];
+            if (ok && num_kb > 0) {
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16), v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            }
+            // The up half of the tile is handed to the gate half through the first stage of the ring, which
+            // nothing reads any more (static shared memory of its own would cost the second CTA per SM).
+            float (*up_rows)[17] = reinterpret_cast<float (*)[17]>(smem);
+            if (row >= 64) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) up_rows[row - 64][j] = v[j];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps, on every path
+            if (ok && row < 64) {
+                const int col = m0 / 2 + row;                        // column of the inner activation
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int c = n0 + j;
+                    if (c < N) {
+                        // as the unfused path: both products rounded to bfloat16, the activation in float32
+                        const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
+                        const float u = __bfloat162float(__float2bfloat16_rn(up_rows[row][j]));
+                        out[static_cast<size_t>(c) * ldo + col] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                    }
+                }
+            }
+        } else if (ok) {
 #pragma unroll
             for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
                 float v[16];
@@ -203,12 +236,12 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int BLOCK_N, int STAGES, bool TRANSPOSED, typename OutT>
+template <int BLOCK_N, int STAGES, bool TRANSPOSED, typename OutT, bool GATED = false>
 int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ldo, int M, int N, int K, int splits,
            float* partials, int* tickets, int* status, cudaStream_t stream) {
     constexpr int smem = STAGES * (kBlockM * kBlockK * 2 + BLOCK_N * kBlockK * 2) + 1024;
     static bool configured = false;
-    auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, TRANSPOSED, OutT>;   // swapped use: A holds weights
+    auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, TRANSPOSED, OutT, GATED>;   // swapped use: A holds weights
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -287,6 +320,23 @@ int stride_gemm_tc_skinny(const void* x, const void* w, void* out, int tokens, i
         default: return STRIDE_TC_LAUNCH(256, 4);
     }
 #undef STRIDE_TC_LAUNCH
+}
+
+// out = silu(x @ gate^T) * (x @ up^T) for at most 16 tokens. w: [2 * inner, k] bf16 with the rows of gate and up
+// alternating in blocks of 64 (gate 0-63, up 0-63, gate 64-127, ...); out: [tokens, inner] bf16. Returns -2 for
+// what it does not take (inner % 64 != 0, more than 16 tokens, sizes for which K would be split, unaligned
+// operands); the caller then runs the product and the activation separately.
+int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, int inner, int k, int* status, cudaStream_t stream) {
+    if (tokens < 0 || inner <= 0 || k <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    if (status == nullptr) return STRIDE_BAD_ARGUMENT;
+    if (tokens > 16 || inner % 64 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
+    if (stride_gemm_tc_splits(2 * inner, tokens, k) != 1) return STRIDE_UNSUPPORTED;
+    const CUtensorMap* map_a = tc::cached_map(w, 2 * inner, k, k, tc::kBlockM);
+    const CUtensorMap* map_b = tc::cached_map(x, tokens, k, k, 16);
+    if (!map_a || !map_b) return STRIDE_UNSUPPORTED;
+    return tc::launch<16, 6, true, __nv_bfloat16, true>(map_a, map_b, static_cast<__nv_bfloat16*>(out), inner, 2 * inner, tokens, k, 1,
+                                                        nullptr, nullptr, status, stream);
 }
 
 }  // extern "C"

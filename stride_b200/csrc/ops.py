@@ -33,7 +33,8 @@ _SIGNATURES = {
     "stride_add_residual": ("elementwise", [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
     "stride_rope_kv_write": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_gemm_tc_gated": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -79,7 +80,14 @@ def _check(code: int, name: str) -> None:
     raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle. Asked for on every launch, so through the one C call when torch has it
+    (``torch.cuda.current_stream()`` builds a Python object every time)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -150,11 +158,14 @@ def rope_kv_write(qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages
            "rope_kv_write")
 
 
-def silu_mul(inp, out) -> None:
+def silu_mul(inp, out, block: int | None = None) -> None:
+    """``out = silu(gate) * up`` for ``inp`` = [tokens, 2 * inter] whose gate and up columns alternate in
+    blocks of ``block`` columns (default: all gate columns, then all up columns)."""
     tokens, inter = out.shape
     if inp.shape != (tokens, 2 * inter) or inp.dtype != out.dtype:
         raise KernelError("silu_mul wants [tokens, 2*inter] in and [tokens, inter] out of one element type")
-    _check(_fn("stride_silu_mul")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, _code(out.dtype), _stream()), "silu_mul")
+    _check(_fn("stride_silu_mul")(_dev(inp, "in"), _dev(out, "out"), tokens, inter, inter if block is None else int(block),
+                                  _code(out.dtype), _stream()), "silu_mul")
 
 
 # ----------------------------------------------------------------------- matmul
@@ -243,6 +254,26 @@ def linear_tc(x, weight, out) -> bool:
     if code == -2:
         return False
     _check(code, "gemm_tc_skinny")
+    return True
+
+
+GATED_BLOCK = 64      # rows of gate and up alternate in blocks of this many in a weight laid out for ``linear_gated_tc``
+
+
+def linear_gated_tc(x, weight, out) -> bool:
+    """``out = silu(x @ gate.T) * (x @ up.T)`` in one tcgen05 kernel for at most 16 rows of ``x``; ``weight`` is
+    [2 * inter, k] with gate and up rows alternating in blocks of ``GATED_BLOCK``. Returns False when the kernel
+    does not take the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
+    m, k = x.shape
+    inter = weight.shape[0] // 2
+    if m > TC_GEMM_MAX_TOKENS or out.shape != (m, inter):
+        return False
+    st = _tc_buffers(x.device, 0)
+    code = _fn("stride_gemm_tc_gated")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
+                                       _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_tc_gated")
     return True
 
 

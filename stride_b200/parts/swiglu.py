@@ -1,6 +1,11 @@
 """Dense gated feed-forward: ``down(silu(gate(x)) * up(x))``
 (python/stride_worker/layers.py:152-161). Gate and up are one matrix product
-(their weights are stacked at load time); SiLU and the product run in float32."""
+(their weights are stacked at load time); SiLU and the product run in float32.
+
+In bfloat16, when the inner width allows it, the stacked weight alternates 64 rows
+of gate and 64 rows of up, so that a 128-row tile of the decode product holds both
+halves of 64 activations and its epilogue can apply SiLU and the product itself;
+``silu_mul`` reads the same layout after the library product of a prefill."""
 
 from __future__ import annotations
 
@@ -8,6 +13,13 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, TensorDecl, register_part
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
+    """[2 * inter, hidden]: ``block`` rows of gate, ``block`` rows of up, and so on (block == inter: plain stacking)."""
+    inter, hidden = gate.shape
+    return torch.stack([gate.view(inter // block, block, hidden), up.view(inter // block, block, hidden)], dim=1) \
+        .reshape(2 * inter, hidden).contiguous()
 
 
 class SwiGLU(FeedForward):
@@ -29,19 +41,23 @@ class SwiGLU(FeedForward):
 
     def bind(self, weights):
         g, u, d = self._names()
-        self.w_gate_up = torch.cat([weights[g], weights[u]], dim=0).contiguous()
+        gate, up = weights[g], weights[u]
+        self.block = ops.GATED_BLOCK if (gate.dtype == torch.bfloat16 and self.inter % ops.GATED_BLOCK == 0) else self.inter
+        self.w_gate_up = interleave_gate_up(gate, up, self.block)
         self.w_down = weights[d]
 
     def named_tensors(self):
         g, u, d = self._names()
-        return {g: self.w_gate_up[:self.inter], u: self.w_gate_up[self.inter:], d: self.w_down}
+        blocks = self.w_gate_up.view(self.inter // self.block, 2, self.block, self.hidden)
+        return {g: blocks[:, 0].reshape(self.inter, self.hidden), u: blocks[:, 1].reshape(self.inter, self.hidden), d: self.w_down}
 
     def forward(self, x, ctx):
         tokens = x.shape[0]
-        gate_up = self.rt.buffer("gate_up", tokens, 2 * self.inter)
-        ops.linear(x, self.w_gate_up, gate_up)
         act = self.rt.buffer("ffn_act", tokens, self.inter)
-        ops.silu_mul(gate_up, act)
+        if not (self.block == ops.GATED_BLOCK and ops.linear_gated_tc(x, self.w_gate_up, act)):
+            gate_up = self.rt.buffer("gate_up", tokens, 2 * self.inter)
+            ops.linear(x, self.w_gate_up, gate_up)
+            ops.silu_mul(gate_up, act, self.block)
         out = self.rt.buffer("ffn_out", tokens, self.hidden)
         ops.linear(act, self.w_down, out)
         return out

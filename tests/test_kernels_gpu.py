@@ -172,6 +172,53 @@ def test_silu_mul(ops, dtype):
     close(out, gate * torch.sigmoid(gate) * up, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,block", [(192, 64), (136, 4), (320, 5)])
+def test_silu_mul_with_gate_and_up_in_alternating_blocks(ops, dtype, inter, block):
+    g = torch.Generator().manual_seed(8)
+    gate = (torch.randn(7, inter, generator=g) * 4).to(dtype)
+    up = (torch.randn(7, inter, generator=g) * 4).to(dtype)
+    x = torch.stack([gate.view(7, inter // block, block), up.view(7, inter // block, block)], dim=2).reshape(7, 2 * inter)
+    out = torch.empty(7, inter, dtype=dtype, device="cuda")
+    ops.silu_mul(dev(x.contiguous()), out, block)
+    close(out, gate.double() * torch.sigmoid(gate.double()) * up.double(), dtype)
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(8, 14336, 4096), (3, 9472, 192), (16, 14336, 1000), (1, 14336, 4096)])
+def test_tcgen05_product_with_gate_epilogue(ops, tokens, inter, k):
+    from stride_b200.parts.swiglu import interleave_gate_up
+
+    g = torch.Generator().manual_seed(33)
+    x = torch.randn(tokens, k, generator=g).bfloat16()
+    gate = (torch.randn(inter, k, generator=g) * 0.05).bfloat16()
+    up = (torch.randn(inter, k, generator=g) * 0.05).bfloat16()
+    # the unfused path: each product rounded to bfloat16, then the activation (python/stride_worker/layers.py:152-161)
+    gx = (x.double() @ gate.double().T).bfloat16().double()
+    ux = (x.double() @ up.double().T).bfloat16().double()
+    want = torch.nn.functional.silu(gx) * ux
+    w = dev(interleave_gate_up(gate, up, ops.GATED_BLOCK))
+    out = torch.full((tokens, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_gated_tc(dev(x), w, out), "the kernel refused sizes it should take"
+    torch.cuda.synchronize()
+    assert ops.tc_status() == 0
+    close(out, want, torch.bfloat16)
+    # the same weight through the product and the blocked silu_mul gives the same within rounding
+    both = torch.empty(tokens, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    ops.linear(dev(x), w, both)
+    unfused = torch.empty_like(out)
+    ops.silu_mul(both, unfused, ops.GATED_BLOCK)
+    close(out, unfused.double(), torch.bfloat16)
+
+
+def test_tcgen05_product_with_gate_epilogue_refuses_what_it_cannot_run(ops):
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_gated_tc(x, torch.zeros(2 * 96, 64, dtype=torch.bfloat16, device="cuda"),
+                                   torch.zeros(4, 96, dtype=torch.bfloat16, device="cuda"))          # inner % 64 != 0
+    x = torch.zeros(4, 1024, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_gated_tc(x, torch.zeros(2 * 128, 1024, dtype=torch.bfloat16, device="cuda"),
+                                   torch.zeros(4, 128, dtype=torch.bfloat16, device="cuda"))         # so few tiles that K would be split
+
+
 def _paged_case(g, dtype, seqs, nq, nkv, hd, page, window=None, spike=None):
     """seqs: list of (context_before, new_tokens). Builds scattered pages that hold
     the keys and values of every token and returns what the kernel needs together
