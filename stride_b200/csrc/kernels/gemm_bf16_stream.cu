@@ -36,11 +36,28 @@ struct Ring {
     static constexpr int kStages = NT == 1 ? 4 : 3;      // 96 KB of ring per 256-thread CTA either way (deeper or shallower rings measured the same)
 };
 
-// NT: token tiles of eight. MODE 0: bfloat16 output, 1: float32 output.
+// What the projection of queries, keys and values does with its result instead of storing it (MODE 2): bias,
+// rotation of queries and keys by the token's position (pairs (i, i + hd/2), float32 tables
+// [position][hd/2]: python/stride_worker/layers.py:85-106), queries back into `out`, keys and values into
+// the token's slot of the paged cache (python/stride_worker/cache.py:58-90, pages [page][kv head][slot][hd]).
+struct QkvEpilogue {
+    const float* bias;                 // [(nq + 2 nkv) * hd] or null
+    const int32_t* positions;          // [tokens]
+    const int32_t* slot_mapping;       // [tokens], page * page_size + offset, negative: store nothing; null: store nothing
+    const float* cos_table;
+    const float* sin_table;
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    int nq, nkv, hd, page_size, rotate;
+};
+
+// NT: token tiles of eight. MODE 0: bfloat16 output, 1: float32 output, 2: the QKV projection with QkvEpilogue:
+// a CTA then owns eight rotation pairs of one head, rows p..p+7 and p + hd/2..p + hd/2 + 7, so that both
+// halves of a pair meet in its epilogue.
 template <int NT, int WARPS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int m, int n,
-                   int k) {
+                   int k, const QkvEpilogue qkv) {
     constexpr int STAGES = Ring<NT>::kStages;
     constexpr int THREADS = WARPS * 32;
     constexpr int PIECES = 2 + NT;           // per step: rows g and g + 8 of the weights, then one piece of x per token tile
@@ -50,8 +67,15 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * kRows;
-    const __nv_bfloat16* w_lo = w + static_cast<size_t>(min(r0 + g, n - 1)) * k + 8 * t;
-    const __nv_bfloat16* w_hi = w + static_cast<size_t>(min(r0 + g + 8, n - 1)) * k + 8 * t;
+    int row_lo = r0, row_hi = r0 + 8;                      // first weight row of fragment rows 0-7 and of rows 8-15
+    if (MODE == 2) {
+        const int per_head = qkv.hd / kRows;               // CTAs per head
+        const int head = blockIdx.x / per_head;
+        row_lo = head * qkv.hd + (blockIdx.x - head * per_head) * 8;
+        row_hi = row_lo + qkv.hd / 2;
+    }
+    const __nv_bfloat16* w_lo = w + static_cast<size_t>(min(row_lo + g, n - 1)) * k + 8 * t;
+    const __nv_bfloat16* w_hi = w + static_cast<size_t>(min(row_hi + g, n - 1)) * k + 8 * t;
     const int steps = (k + kStepCols - 1) / kStepCols;
     // K is dealt out in batches of kUnroll consecutive steps, batch b to warp b % WARPS
     const int batches = (steps + kUnroll - 1) / kUnroll;
@@ -130,7 +154,53 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         red[warp][nt][g + 8][2 * t + 1] = acc[nt][3];
     }
     __syncthreads();
-    {
+    if (MODE == 2) {
+        // one thread per (token, pair): same arithmetic as rope_kv_write_kernel on the product rounded to bfloat16
+        const int head = row_lo / qkv.hd, i0 = row_lo - head * qkv.hd, half = qkv.hd / 2;
+        for (int i = threadIdx.x; i < NT * 8 * 8; i += THREADS) {
+            const int c = i & 7, token = i >> 3;
+            if (token >= m) continue;
+            const int nt = token >> 3, tk = token & 7;
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int wp = 0; wp < WARPS; ++wp) {
+                a += red[wp][nt][c][tk];
+                b += red[wp][nt][c + 8][tk];
+            }
+            a = __bfloat162float(__float2bfloat16_rn(a));
+            b = __bfloat162float(__float2bfloat16_rn(b));
+            const int idx = i0 + c;                        // index of the pair's first half inside the head
+            if (qkv.bias) {
+                a = __fadd_rn(a, qkv.bias[head * qkv.hd + idx]);
+                b = __fadd_rn(b, qkv.bias[head * qkv.hd + idx + half]);
+            }
+            if (head < qkv.nq + qkv.nkv && qkv.rotate) {
+                const size_t at = static_cast<size_t>(qkv.positions[token]) * half + idx;
+                const float cs = qkv.cos_table[at], sn = qkv.sin_table[at];
+                const float ra = __fadd_rn(__fmul_rn(a, cs), __fmul_rn(-b, sn));
+                const float rb = __fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn));
+                a = ra;
+                b = rb;
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (head < qkv.nq) {
+                dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(token) * n + head * qkv.hd;
+            } else {
+                const int slot = qkv.slot_mapping ? qkv.slot_mapping[token] : -1;
+                if (slot >= 0) {
+                    const bool is_key = head < qkv.nq + qkv.nkv;
+                    const int kvh = is_key ? head - qkv.nq : head - qkv.nq - qkv.nkv;
+                    const int page = slot / qkv.page_size, offset = slot - page * qkv.page_size;
+                    dst = (is_key ? qkv.k_pages : qkv.v_pages) +
+                          ((static_cast<size_t>(page) * qkv.nkv + kvh) * qkv.page_size + offset) * qkv.hd;
+                }
+            }
+            if (dst) {
+                dst[idx] = __float2bfloat16_rn(a);
+                dst[idx + half] = __float2bfloat16_rn(b);
+            }
+        }
+    } else {
         // one thread per (token, row): the warps' partial sums are added in warp order
         for (int i = threadIdx.x; i < NT * 8 * kRows; i += THREADS) {
             const int row = i & (kRows - 1), token = i / kRows;
@@ -148,7 +218,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 template <int NT, int WARPS, int MODE>
-int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream) {
+int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, const QkvEpilogue& qkv, cudaStream_t stream) {
     constexpr int smem = Ring<NT>::kStages * kUnroll * (2 + NT) * WARPS * 32 * 16;
     auto kernel = gemm_stream_kernel<NT, WARPS, MODE>;
     static bool configured = false;
@@ -157,16 +227,17 @@ int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int 
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(static_cast<unsigned>((n + kRows - 1) / kRows)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k);
+    stride::launch(kernel, dim3(static_cast<unsigned>((n + kRows - 1) / kRows)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, qkv);
     return STRIDE_LAUNCH_STATUS();
 }
 
 template <int NT, int MODE>
-int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream) {
+int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream,
+                  const QkvEpilogue& qkv = QkvEpilogue{}) {
     const int batches = ((k + kStepCols - 1) / kStepCols + kUnroll - 1) / kUnroll;
-    if (batches >= 8 * 4) return launch_warps<NT, 8, MODE>(x, w, out, m, n, k, stream);
-    if (batches >= 4 * 4) return launch_warps<NT, 4, MODE>(x, w, out, m, n, k, stream);
-    return launch_warps<NT, 2, MODE>(x, w, out, m, n, k, stream);
+    if (batches >= 8 * 4) return launch_warps<NT, 8, MODE>(x, w, out, m, n, k, qkv, stream);
+    if (batches >= 4 * 4) return launch_warps<NT, 4, MODE>(x, w, out, m, n, k, qkv, stream);
+    return launch_warps<NT, 2, MODE>(x, w, out, m, n, k, qkv, stream);
 }
 
 }  // namespace stream_gemm
@@ -189,4 +260,25 @@ extern "C" int stride_gemm_stream_bf16(const void* x, const void* w, void* out, 
                           : stream_gemm::launch_stream<1, 0>(xp, wp, out, tokens, n_out, k, stream);
     return out_is_f32 ? stream_gemm::launch_stream<2, 1>(xp, wp, out, tokens, n_out, k, stream)
                       : stream_gemm::launch_stream<2, 0>(xp, wp, out, tokens, n_out, k, stream);
+}
+
+// The projection of queries, keys and values for at most 16 tokens with rotation and cache write in its
+// epilogue: qkv_out [tokens, (nq + 2 nkv) * hd] receives the rotated queries (its key and value columns are
+// not written), the rotated keys and the values go to the page slots of slot_mapping. Arguments as
+// stride_rope_kv_write. Returns -2 for what it does not take (hd % 16 != 0, more than 16 tokens, unaligned
+// operands); the caller then runs the product and stride_rope_kv_write.
+extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* qkv_out, const float* bias, const int32_t* positions,
+                                           const int32_t* slot_mapping, const float* cos_table, const float* sin_table,
+                                           void* k_pages, void* v_pages, int tokens, int nq, int nkv, int hd, int page_size,
+                                           int k, int rotate, cudaStream_t stream) {
+    if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || k <= 0 || positions == nullptr) return STRIDE_BAD_ARGUMENT;
+    if (tokens > 16 || hd % 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
+    if (tokens == 0) return 0;
+    stream_gemm::QkvEpilogue e{bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages),
+                               static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate};
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    auto wp = static_cast<const __nv_bfloat16*>(w);
+    const int n_out = (nq + 2 * nkv) * hd;
+    if (tokens <= 8) return stream_gemm::launch_stream<1, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e);
+    return stream_gemm::launch_stream<2, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e);
 }

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_gemm_stream_qkv_rope": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
@@ -287,6 +289,26 @@ def linear_stream(x, weight, out) -> bool:
     if code == -2:
         return False
     _check(code, "gemm_stream_bf16")
+    return True
+
+
+def linear_qkv_rope(x, weight, qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages, nq: int, nkv: int, hd: int,
+                    page_size: int, rotate: bool) -> bool:
+    """The projection of queries, keys and values with ``rope_kv_write`` in its epilogue, for at most 16 rows of
+    ``x``: afterwards ``qkv`` holds the rotated queries (its key and value columns are not written) and the cache
+    the rotated keys and the values. Returns False when the kernel does not take the sizes; the caller then runs
+    ``linear`` and ``rope_kv_write``."""
+    m, k = x.shape
+    if not STREAM_GEMM or m > TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16 or qkv.shape != (m, (nq + 2 * nkv) * hd):
+        return False
+    code = _fn("stride_gemm_stream_qkv_rope")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(qkv, "qkv", torch.bfloat16),
+        _opt(bias, "bias", torch.float32), _dev(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_stream_qkv_rope")
     return True
 
 

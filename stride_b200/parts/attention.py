@@ -74,14 +74,28 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache):
         tokens = x.shape[0]
         qkv = self.rt.buffer("qkv", tokens, self.qkv_dim)
-        ops.linear(x, self.w_qkv, qkv)
-        self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
+        if not self._project_and_rotate(x, qkv, ctx, cache, tokens):
+            ops.linear(x, self.w_qkv, qkv)
+            self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
         attn = self.rt.buffer("attn", tokens, self.q_dim)
         self._attend(qkv, attn, ctx, cache, tokens)
         out = self.rt.buffer("mixer_out", tokens, self.hidden)
         ops.linear(attn, self.w_o, out)
         return out
 
+
+    def _project_and_rotate(self, x, qkv, ctx, cache, tokens) -> bool:
+        """A decode step's projection with the position encoding and the cache write in its epilogue, when the
+        position part says that what it does is the standard rotation. False: nothing was done."""
+        if tokens > ops.TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16:
+            return False
+        tables = self.position.rotation_tables()
+        if tables is None:
+            return False
+        cos, sin, rotate = tables
+        slots = ctx.slot_mapping[cache.group][:tokens] if cache.writes else None
+        return ops.linear_qkv_rope(x, self.w_qkv, qkv, self.bias, ctx.positions[:tokens], slots, cos, sin, cache.k_pages,
+                                   cache.v_pages, self.nq, self.nkv, self.hd, cache.page_size, rotate)
 
     def _attend(self, qkv, attn, ctx, cache, tokens):
         table = ctx.block_table[cache.group]

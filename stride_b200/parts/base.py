@@ -96,6 +96,12 @@ class PositionEncoding(Part):
     def encode_and_store(self, qkv, bias, ctx, cache, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         raise NotImplementedError
 
+    def rotation_tables(self):
+        """Optional. ``(cos, sin, rotate)`` if what ``encode_and_store`` does is the pairwise rotation of
+        ``ops.rope_kv_write`` with these float32 tables (``rotate`` False: no rotation, only the store); a
+        mixer may then fold it into its projection. ``None`` (the default): call ``encode_and_store``."""
+        return None
+
 
 class Mixer(Part):
     def cache_request(self) -> Optional[CacheRequest]:

@@ -55,6 +55,10 @@ class RotaryEncoding(PositionEncoding):
             self._tables = self.rt.shared(("rope", self.spec), self._build)
         return self._tables
 
+    def rotation_tables(self):
+        cos, sin = self.tables()
+        return cos, sin, True
+
     def encode_and_store(self, qkv, bias, ctx, cache, num_heads, num_kv_heads, head_dim):
         cos, sin = self.tables()
         ops.rope_kv_write(qkv, bias, ctx.positions[:qkv.shape[0]],
@@ -70,6 +74,9 @@ class NoPositionEncoding(PositionEncoding):
         super().__init__(spec, runtime)
         self.max_positions = int(spec.max_positions) if spec.max_positions else 1
         self._dummy = runtime.shared(("rope-dummy",), lambda: torch.zeros(8, dtype=torch.float32, device=runtime.device))
+
+    def rotation_tables(self):
+        return self._dummy, self._dummy, False
 
     def encode_and_store(self, qkv, bias, ctx, cache, num_heads, num_kv_heads, head_dim):
         ops.rope_kv_write(qkv, bias, ctx.positions[:qkv.shape[0]],

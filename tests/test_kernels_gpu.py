@@ -469,6 +469,45 @@ def test_streaming_product_for_few_tokens(ops, tokens, n_out, k):
         assert float(out[tokens].min()) == 7.0, "the kernel wrote past the last token"
 
 
+@pytest.mark.parametrize("tokens,nq,nkv,hd,k,page,bias,rotate", [
+    (8, 32, 8, 128, 4096, 16, False, True), (3, 5, 5, 48, 88, 16, True, True), (16, 6, 2, 16, 200, 8, False, True),
+    (11, 4, 1, 128, 192, 16, True, False), (1, 3, 1, 64, 96, 32, False, True),
+])
+def test_streaming_projection_with_rotation_and_cache_write(ops, tokens, nq, nkv, hd, k, page, bias, rotate):
+    """The fused kernel against the product followed by ``rope_kv_write`` (itself tested against float64)."""
+    g = torch.Generator().manual_seed(34)
+    heads = nq + 2 * nkv
+    x = dev(torch.randn(tokens, k, generator=g).bfloat16())
+    w = dev((torch.randn(heads * hd, k, generator=g) * 0.05).bfloat16())
+    b = dev(torch.randn(heads * hd, generator=g) * 0.1) if bias else None
+    num_pages, max_pos = 9, 700
+    positions = dev(torch.randint(0, max_pos, (tokens,), generator=g).to(torch.int32))
+    slots = torch.randperm(num_pages * page, generator=g)[:tokens].to(torch.int32)
+    if tokens > 2:
+        slots[tokens - 1] = -1                       # a padded token stores nothing
+    slots = dev(slots)
+    inv = plain.rope_inv_freq(hd, 25000.0, None)
+    angles = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    cos, sin = dev(angles.cos()), dev(angles.sin())
+
+    def run(fused):
+        k_pages = torch.full((num_pages, nkv, page, hd), 3.0, dtype=torch.bfloat16, device="cuda")
+        v_pages = torch.full_like(k_pages, 3.0)
+        qkv = torch.full((tokens, heads * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            assert ops.linear_qkv_rope(x, w, qkv, b, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, rotate)
+        else:
+            ops.linear_stream(x, w, qkv)
+            ops.rope_kv_write(qkv, b, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, rotate=rotate)
+        torch.cuda.synchronize()
+        return qkv[:, :nq * hd].clone(), k_pages, v_pages
+
+    q1, k1, v1 = run(True)
+    q0, k0, v0 = run(False)
+    assert torch.equal(q1, q0) and torch.equal(k1, k0) and torch.equal(v1, v0), "the fused projection differs from product + rope_kv_write"
+    assert float(k1.float().sub(3.0).abs().max()) > 0.0     # something was stored
+
+
 def test_streaming_product_refuses_what_it_cannot_run(ops):
     w = torch.zeros(128, 100, dtype=torch.bfloat16, device="cuda")
     assert not ops.linear_stream(torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda"), w,
