@@ -50,6 +50,8 @@ class _Staging:
 
 
 class ModelRunner:
+    CONTEXT_BUCKET_BASE = 2048      # the smallest context bound a decode graph is captured for
+
     def __init__(self, model, cache_manager, *, token_capacity: int, seq_capacity: int, row_capacity: int,
                  max_model_len: int, cuda_graphs: bool = True):
         ops.require_device()
@@ -65,7 +67,8 @@ class ModelRunner:
                                                           self.table_width), self.device)
         self.cuda_graphs = cuda_graphs and model.graph_safe
         self._decode_buckets = _buckets(min(seq_capacity, token_capacity))
-        self._graphs: dict[int, tuple] = {}
+        self._graphs: dict[tuple, tuple] = {}        # (batch bucket, context bucket) -> (graph, logits)
+        self._stagings: dict[int, _Staging] = {}     # batch bucket -> packed step arrays
         self.steps = 0
         self.graph_replays = 0
         self.last_h2d_bytes = 0
@@ -93,7 +96,7 @@ class ModelRunner:
         return self._step_eager(batch, to_host)
 
     # ------------------------------------------------------------------- eager
-    def _context(self, staging, batch, num_tokens, num_rows, for_graph=False):
+    def _context(self, staging, batch, num_tokens, num_rows, for_graph: int = 0):
         items, row = [], 0
         for request, tokens, position, _want in batch.items():
             items.append((request, row, len(tokens), position, self.cache.state_slot(request)))
@@ -102,7 +105,7 @@ class ModelRunner:
         while tail_seq > 0 and items[tail_seq - 1][2] == 1:
             tail_seq -= 1
         tail_start = items[tail_seq][1] if tail_seq < len(items) else row
-        bound = self.table_width * self.cache.page_size if for_graph else batch.max_ctx
+        bound = for_graph if for_graph else batch.max_ctx       # a captured graph is sized for its context bucket
         return make_context(staging.dev, staging.layout, num_tokens, batch.num_seqs, num_rows, max_q_len=batch.max_q_len,
                             max_ctx=batch.max_ctx, decode_only=batch.decode_only, host_items=items,
                             decode_tail_start=0 if for_graph else tail_start, decode_tail_seq=0 if for_graph else tail_seq,
@@ -158,13 +161,28 @@ class ModelRunner:
                 return b
         return self._decode_buckets[-1]
 
+    def _context_bucket(self, max_ctx: int) -> int:
+        """The context bound a decode graph is captured for: 2048, 3072, 4096, 5120, 7168, 9216, ... (a quarter
+        more each time, in steps of 1024), at most what the block table holds. Kernels size their grids and
+        choose their splits from the bound, so a short context does not pay for max_model_len; a growing one
+        moves to the next graph every 25 % of its length."""
+        full = self.table_width * self.cache.page_size
+        step = max(1, self.CONTEXT_BUCKET_BASE // 2)
+        bound = self.CONTEXT_BUCKET_BASE
+        while bound < max_ctx and bound < full:
+            bound = -(-(bound * 5 // 4) // step) * step
+        return min(bound, full)
+
     def _step_graph(self, batch):
         b = self._bucket(batch.num_seqs)
-        entry = self._graphs.get(b)
+        cb = self._context_bucket(batch.max_ctx)
+        staging = self._stagings.get(b)
+        if staging is None:
+            staging = self._stagings[b] = _Staging(self._rt_mod.packed_layout(self.groups, b, b, b, self.table_width), self.device)
+        entry = self._graphs.get((b, cb))
         if entry is None:
-            staging = _Staging(self._rt_mod.packed_layout(self.groups, b, b, b, self.table_width), self.device)
             self._pack(staging, batch)
-            ctx = self._context(staging, batch, b, b, for_graph=True)
+            ctx = self._context(staging, batch, b, b, for_graph=cb)
             self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -172,9 +190,9 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
             self.launches_per_graph[b] = ops.counters["launches"] - before
-            entry = (staging, graph, logits)
-            self._graphs[b] = entry
-        staging, graph, logits = entry
+            entry = (graph, logits)
+            self._graphs[(b, cb)] = entry
+        graph, logits = entry
         self._pack(staging, batch)
         graph.replay()
         self.graph_replays += 1
@@ -182,4 +200,4 @@ class ModelRunner:
         return logits[:batch.num_rows]
 
     def captured_buckets(self) -> list[int]:
-        return sorted(self._graphs)
+        return sorted({b for b, _cb in self._graphs})

@@ -131,6 +131,22 @@ def test_long_decoding_and_first_tokens(case, dtype):
             assert session.runner.graph_replays > 100, "decode steps did not go through captured graphs"
 
 
+def test_decoding_across_context_buckets(case, monkeypatch):
+    """A decode graph is captured for a bound on the context; a request that grows past it moves to the graph
+    of the next bound. With a small first bound the 161 tokens of request c cross two of them."""
+    from stride_b200.engine.runner import ModelRunner
+    monkeypatch.setattr(ModelRunner, "CONTEXT_BUCKET_BASE", 16)
+    tokens = case["requests"]["c"]
+    steps = [{"step": 0, "entries": [{"id": "c", "tokens": tokens[:3], "want": [0, 1, 2]}], "end": []}]
+    for p in range(3, len(tokens)):
+        steps.append({"step": p, "entries": [{"id": "c", "tokens": [tokens[p]], "want": [0]}], "end": []})
+    steps[-1]["end"] = ["c"]
+    session = session_for(case, "bfloat16", steps, graphs=True)
+    got = replay(session, steps)
+    check(got, case["want"]["bfloat16"], "bfloat16", "decode across context buckets")
+    assert len({cb for _b, cb in session.runner._graphs}) >= 3, "the context never moved to another graph"
+
+
 def test_an_unknown_token_or_too_few_pages_is_an_error_not_a_wrong_result(case):
     from stride_b200.engine.trace import TraceError, TraceSession
     s = TraceSession(case["dirs"]["float32"], "float32", max_tokens=64, block_size=case["page"])
