@@ -1,7 +1,8 @@
 // Prefill attention in bfloat16 on the fifth-generation tensor cores.
 //
-// One CTA owns 128 consecutive query rows of one request and one query head; two CTAs share
-// an SM. Keys and values are walked in tiles of 64. For each tile
+// One CTA owns 128 consecutive query rows of one request and two query heads that share a key head (one
+// head, and then two CTAs per SM, when the group is odd): both heads use every key and value tile that is
+// loaded. Keys and values are walked in tiles of 64. For each tile and head
 //   S = Q K^T        tcgen05.mma, M = 128 queries, N = 64 keys, accumulator in tensor memory
 //   P = softmax part four warps, one thread per query row, read S with tcgen05.ld, keep the
 //                    running maximum and sum in float32, write P (bfloat16 pairs) back into
@@ -17,14 +18,15 @@
 // layout the products expect: a page is small (16 keys of one head are 4 KB) and a TMA copy per
 // page and 64-column half cost more to issue than the softmax of the tile takes (measured: 16
 // copies of 2 KB per tile held the tile at 3300 cycles, the softmax needs 1400), while
-// one warp per stream with cp.async keeps up for any page size. The output accumulator is
+// cp.async by a few warps works the same for any page size. The output accumulator is
 // rescaled only when a row's maximum has grown by more than 2^8 since the value in use, which
 // keeps tensor-memory traffic low and the exponentials bounded. The mask is that of
 // python/stride_worker/layers.py:109-149 (key <= query position) plus an optional window.
 //
-// Roles: warp 0 copies keys, warp 1 issues the products and owns tensor memory, warp 2 copies
-// values, warp 3 fetches Q, warps 4-7 do the softmax and the final store. Every mbarrier wait
-// is bounded; a wait that runs out sets *status.
+// Roles (two heads, 512 threads): warps 0-2 copy keys, warp 3 issues the products and owns tensor memory,
+// warps 4-6 copy values, warp 7 fetches Q, warps 8-15 do the softmax and the final store, four per head.
+// CTAs are dispatched longest first (the grid's fast dimension is the head, the slow one the query tile,
+// last tile first). Every mbarrier wait is bounded; a wait that runs out sets *status.
 #include "tcgen05.cuh"
 #include "mma.cuh"
 
@@ -33,11 +35,13 @@ namespace tc {
 
 constexpr int kQRows = 128;
 constexpr int kKeys = 64;
-constexpr int kAttnThreads = 256;
 constexpr float kRescaleThreshold = 8.f;      // in log2 units
 
-template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 2)
+// HEADS query heads of one key head per CTA (1 or 2). One head: 4 service warps (keys, products, values, Q) and 4
+// softmax warps, two CTAs per SM. Two heads: 8 service warps (three for keys, products, three for values, Q) and
+// 8 softmax warps, one CTA per SM: a single warp cannot issue a tile's copies as fast as two heads consume them.
+template <int HD, int HEADS>
+__global__ void __launch_bounds__(HEADS == 1 ? 256 : 512, HEADS == 1 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfloat16* __restrict__ k_pages,
                        const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                        const int32_t* __restrict__ block_table, int table_width, const int32_t* __restrict__ q_start,
@@ -48,27 +52,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
     constexpr int KV_HALF_BYTES = kKeys * 128;            // [64 keys x 64 columns] of K or V
     constexpr int Q_BYTES = HALVES * HALF_BYTES;
     constexpr int KV_BYTES = HALVES * KV_HALF_BYTES;      // one K tile or one V tile
-    constexpr uint32_t TMEM_COLS = 256;                   // two score buffers (P over S) of 64 columns, O: HD columns
+    constexpr uint32_t HEAD_COLS = 256;                   // per head: two score buffers (P over S) of 64 columns, O: HD columns
+    constexpr uint32_t TMEM_COLS = HEAD_COLS * HEADS;
+    constexpr int KS = HEADS == 1 ? 2 : 4;                // stages of the key ring and of the value ring
+    constexpr int LOADERS = HEADS == 1 ? 1 : 3;           // warps per copy stream
+    constexpr int MMA_WARP = LOADERS, Q_WARP = 2 * LOADERS + 1, SERVICE_WARPS = 2 * LOADERS + 2;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_s = smem;
-    unsigned char* k_s = q_s + Q_BYTES;                   // two key tiles, then two value tiles
-    unsigned char* v_s = k_s + 2 * KV_BYTES;
-    __shared__ __align__(8) uint64_t q_full, pv_done;
-    __shared__ __align__(8) uint64_t s_full[2], p_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2];
+    unsigned char* q_s = smem;                            // HEADS query tiles
+    unsigned char* k_s = q_s + HEADS * Q_BYTES;           // KS key tiles, then KS value tiles
+    unsigned char* v_s = k_s + KS * KV_BYTES;
+    __shared__ __align__(8) uint64_t q_full, pv_done[HEADS];
+    __shared__ __align__(8) uint64_t s_full[HEADS][2], p_full[HEADS][2], k_full[KS], k_empty[KS], v_full[KS], v_empty[KS];
     __shared__ uint32_t tmem_base_slot;
 
     pdl_trigger();
-    // Which request and which of its query tiles is this CTA? Within a request the last tile, which
-    // has the most keys to walk, comes first in the grid, so that the long CTAs do not form the tail.
+    // Which request and which of its query tiles is this CTA? blockIdx.y counts the tiles, blockIdx.x the heads:
+    // CTAs are handed out x first, so all heads of a tile start together, and within a request the last tile,
+    // which has the most keys to walk, comes first: the long CTAs start first and do not form the tail.
     int seq = -1, tile = 0;
     {
         int acc = 0;
         for (int s = 0; s < num_seqs; ++s) {
             const int tiles = (q_len[s] + kQRows - 1) / kQRows;
-            if (static_cast<int>(blockIdx.x) < acc + tiles) {
+            if (static_cast<int>(blockIdx.y) < acc + tiles) {
                 seq = s;
-                tile = tiles - 1 - (blockIdx.x - acc);
+                tile = tiles - 1 - (blockIdx.y - acc);
                 break;
             }
             acc += tiles;
@@ -76,7 +85,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
     }
     if (seq < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y, kvh = head / (nq / nkv);
+    const int head0 = blockIdx.x * HEADS, kvh = head0 / (nq / nkv);      // heads head0 .. head0 + HEADS - 1 share the key head
     const int n_q = q_len[seq];
     const int row0 = tile * kQRows;
     const int rows = min(kQRows, n_q - row0);
@@ -90,29 +99,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
-        mbar_init(smem_u32(&pv_done), 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&p_full[s]), 4);
-            mbar_init(smem_u32(&k_full[s]), 32);       // one arrival per lane of the copying warp
+        for (int h = 0; h < HEADS; ++h) {
+            mbar_init(smem_u32(&pv_done[h]), 1);
+            for (int s = 0; s < 2; ++s) {
+                mbar_init(smem_u32(&s_full[h][s]), 1);
+                mbar_init(smem_u32(&p_full[h][s]), 4);
+            }
+        }
+        for (int s = 0; s < KS; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 32 * LOADERS);       // one arrival per lane of the copying warps
             mbar_init(smem_u32(&k_empty[s]), 1);
-            mbar_init(smem_u32(&v_full[s]), 32);
+            mbar_init(smem_u32(&v_full[s]), 32 * LOADERS);
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_base_slot, tmem_o = tmem_base_slot + 2 * kKeys;     // score buffer b at tmem_s + b * kKeys
+    // head h: score buffer b at tmem_base + h * HEAD_COLS + b * kKeys, output at + 2 * kKeys
+    const uint32_t tmem_base = tmem_base_slot;
     pdl_wait();       // queries, keys and values were written by the kernels before this one
 
-    if (warp == 0 || warp == 2) {
-        // ---- copying warps: warp 0 walks the key tiles, warp 2 the value tiles. A lane owns one 16-byte
-        // chunk position of the row (cc) and every (32 / chunks per row)-th key; the block table is read
-        // 32 pages at a time, one entry per lane, and handed round by shuffle.
-        const bool is_k = warp == 0;
+    if (warp < SERVICE_WARPS && warp != MMA_WARP && warp != Q_WARP) {
+        // ---- copying warps: the first LOADERS warps walk the key tiles, the LOADERS after the issuer the value
+        // tiles, each taking every LOADERS-th group of rows. A lane owns one 16-byte chunk position of the row
+        // (cc) and every (32 / chunks per row)-th key; the block table is read 32 pages at a time, one entry
+        // per lane, and handed round by shuffle.
+        const bool is_k = warp < MMA_WARP;
+        const int part = is_k ? warp : warp - MMA_WARP - 1;
         const __nv_bfloat16* pages = is_k ? k_pages : v_pages;
         unsigned char* ring = is_k ? k_s : v_s;
         uint64_t* full = is_k ? k_full : v_full;
@@ -125,8 +141,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
         const uint32_t dst_lane = static_cast<uint32_t>((cc >> 3) * KV_HALF_BYTES);
         int win_at = -1, win_entry = 0;
         for (int j = 0; j < n_tiles; ++j) {
-            const int st = j & 1;
-            if (!mbar_wait(smem_u32(&empty[st]), (static_cast<uint32_t>(j >> 1) & 1u) ^ 1u, status, is_k ? 11 : 18)) break;
+            const int st = j % KS;
+            if (!mbar_wait(smem_u32(&empty[st]), (static_cast<uint32_t>(j / KS) & 1u) ^ 1u, status, is_k ? 11 : 18)) break;
             const int k0 = (kt_first + j) * kKeys;
             {   // a tile never straddles a window of 32 pages (tiles and windows are aligned)
                 const int at = ((k0 >> page_shift) - first_page) >> 5;
@@ -138,7 +154,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
             }
             unsigned char* dst_tile = ring + st * KV_BYTES + dst_lane;
 #pragma unroll 4
-            for (int it = 0; it < kKeys / RPI; ++it) {
+            for (int it = part; it < kKeys / RPI; it += LOADERS) {
                 const int r = it * RPI + sub;
                 const int key = k0 + r;
                 const bool valid = key >= first_key && key <= last_pos;      // other rows keep what they held: masked (K) or cleared (V) later
@@ -152,59 +168,74 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
             cp_async_arrive_noinc(smem_u32(&full[st]));
         }
         cp_async_wait<0>();
-    } else if (warp == 3) {
+    } else if (warp == Q_WARP) {
         if (lane == 0) {       // ---- Q: one box per 64 columns
             const uint32_t qb = smem_u32(&q_full);
-            mbar_expect_tx(qb, Q_BYTES);
-            for (int h = 0; h < HALVES; ++h) tma_load_2d(smem_u32(q_s + h * HALF_BYTES), &map_q, qb, head * HD + h * 64, q_row0);
+            mbar_expect_tx(qb, HEADS * Q_BYTES);
+            for (int hh = 0; hh < HEADS; ++hh)
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(smem_u32(q_s + hh * Q_BYTES + h * HALF_BYTES), &map_q, qb, (head0 + hh) * HD + h * 64, q_row0);
         }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
         if (lane == 0) {
             // ---- tensor-core issuer. The scores of tile j+2 are issued right after the output product of
             // tile j, so the softmax of tile j+1 always finds its scores ready and overlaps both.
             constexpr uint32_t idesc_qk = instr_desc_bf16(kQRows, kKeys, false);
             constexpr uint32_t idesc_pv = instr_desc_bf16(kQRows, HD, true);
-            auto scores = [&](int j) {
-                const int st = j & 1;
-                if (!mbar_wait(smem_u32(&k_full[st]), static_cast<uint32_t>(j >> 1) & 1u, status, 13)) return false;
-                fence_proxy_async();         // the keys were written by cp.async, the product reads them through the async proxy
+            auto scores = [&](int j) {      // S = Q K^T of tile j for every head of the CTA
+                const int st = j % KS;
+                if (!mbar_wait(smem_u32(&k_full[st]), static_cast<uint32_t>(j / KS) & 1u, status, 13)) return false;
+                // (cp.async data whose arrival the mbarrier has reported needs no proxy fence before tcgen05.mma reads it)
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(k_s + st * KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {      // S = Q K^T, 16 head columns per product
-                    umma_bf16(tmem_s + st * kKeys, smem_desc(smem_u32(q_s) + (kk / 4) * HALF_BYTES + (kk % 4) * 32, 16, 1024),
-                              smem_desc(k_addr + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+                for (int h = 0; h < HEADS; ++h) {
+                    const uint32_t q_addr = smem_u32(q_s + h * Q_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {      // 16 head columns per product
+                        umma_bf16(tmem_base + h * HEAD_COLS + (j & 1) * kKeys,
+                                  smem_desc(q_addr + (kk / 4) * HALF_BYTES + (kk % 4) * 32, 16, 1024),
+                                  smem_desc(k_addr + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&s_full[h][j & 1]));
                 }
                 umma_commit(smem_u32(&k_empty[st]));         // these keys may be replaced
-                umma_commit(smem_u32(&s_full[st]));
                 return true;
             };
             bool ok = mbar_wait(smem_u32(&q_full), 0, status, 12);
             if (ok) ok = scores(0);
             if (ok && n_tiles > 1) ok = scores(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j & 1;
+                const int st = j % KS;
                 const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
-                ok = mbar_wait(smem_u32(&v_full[st]), ph, status, 19);
-                ok = ok && mbar_wait(smem_u32(&p_full[st]), ph, status, 14);
-                if (!ok) break;
-                fence_proxy_async();
-                tc_fence_after();
+                ok = mbar_wait(smem_u32(&v_full[st]), static_cast<uint32_t>(j / KS) & 1u, status, 19);
                 const uint32_t v_addr = smem_u32(v_s + st * KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < kKeys / 16; ++ks) {   // O += P V, 16 keys per product: P from tensor memory
-                    // (16 bfloat16 = 8 columns per step), V MN-major: 64-column chunks KV_HALF_BYTES apart
-                    umma_bf16_tmem_a(tmem_o, tmem_s + st * kKeys + ks * 8, smem_desc(v_addr + ks * 2048, KV_HALF_BYTES, 1024),
-                                     idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                for (int h = 0; h < HEADS; ++h) {
+                    ok = ok && mbar_wait(smem_u32(&p_full[h][j & 1]), ph, status, 14);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t tmem_h = tmem_base + h * HEAD_COLS;
+#pragma unroll
+                    for (int ks = 0; ks < kKeys / 16; ++ks) {   // O += P V, 16 keys per product: P from tensor memory
+                        // (16 bfloat16 = 8 columns per step), V MN-major: 64-column chunks KV_HALF_BYTES apart
+                        umma_bf16_tmem_a(tmem_h + 2 * kKeys, tmem_h + (j & 1) * kKeys + ks * 8,
+                                         smem_desc(v_addr + ks * 2048, KV_HALF_BYTES, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&pv_done[h]));      // this head's O holds the tile
                 }
+                if (!ok) break;
                 umma_commit(smem_u32(&v_empty[st]));         // these values may be replaced
-                umma_commit(smem_u32(&pv_done));             // O holds this tile
                 // the products run in order, so these scores overwrite P of tile j only after it has been read
                 if (j + 2 < n_tiles) ok = scores(j + 2);
             }
         }
     } else {
-        // ---- softmax and output: warps 4..7 own tensor-memory lanes 0-31, 32-63, 64-95, 96-127
+        // ---- softmax and output: four warps per head, which own tensor-memory lanes 0-31, 32-63, 64-95 and
+        // 96-127 of their head's columns
+        const int hh = (warp - SERVICE_WARPS) >> 2;          // which head of the CTA
+        const int head = head0 + hh;
+        const uint32_t tmem_s = tmem_base + hh * HEAD_COLS, tmem_o = tmem_s + 2 * kKeys;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                    // query row of the tile, also the key row this thread may clear
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -216,7 +247,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
             const uint32_t ph = static_cast<uint32_t>(j >> 1) & 1u;
             const int k0 = (kt_first + j) * kKeys;
             const uint32_t tmem_sj = tmem_s + st * kKeys + lane_base;
-            ok = mbar_wait(smem_u32(&s_full[st]), ph, status, 15);
+            ok = mbar_wait(smem_u32(&s_full[hh][st]), ph, status, 15);
             if (!ok) break;
             tc_fence_after();
             const bool edge = k0 + kKeys - 1 > pos0 || (window > 0 && k0 <= last_pos - window);   // some (row, key) is masked
@@ -257,7 +288,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
                 l *= factor;
                 if (j > 0) {
                     // O belongs to the output product of the tile before until that has finished
-                    ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(j - 1) & 1u, status, 16);
+                    ok = mbar_wait(smem_u32(&pv_done[hh]), static_cast<uint32_t>(j - 1) & 1u, status, 16);
                     if (!ok) break;
                     waited = true;
                     tc_fence_after();
@@ -295,11 +326,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
             // Key rows that no query of this tile may see can hold anything (a page never written, the
             // rest of a page): clear their values, or 0 * garbage would poison the product.
             if (k0 + kKeys - 1 > last_pos || k0 < first_key) {
-                ok = mbar_wait(smem_u32(&v_full[st]), ph, status, 20);
+                // (with two heads both groups of warps clear the same rows with the same zeros: each must be
+                // sure of them before it lets its own product go)
+                const int vst = j % KS;
+                ok = mbar_wait(smem_u32(&v_full[vst]), static_cast<uint32_t>(j / KS) & 1u, status, 20);
                 if (!ok) break;
                 const int key = k0 + row;
                 if (row < kKeys && (key > last_pos || key < first_key)) {
-                    unsigned char* v_row = v_s + st * KV_BYTES + row * 128;
+                    unsigned char* v_row = v_s + vst * KV_BYTES + row * 128;
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h)
 #pragma unroll
@@ -310,12 +344,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
             }
             // Before this warp lets the output product of tile j go: once that one can finish, pv_done may be
             // two phases on and its parity says nothing any more.
-            if (!waited) ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(j - 1) & 1u, status, 21);
+            if (!waited) ok = mbar_wait(smem_u32(&pv_done[hh]), static_cast<uint32_t>(j - 1) & 1u, status, 21);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full[st]));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[hh][st]));
         }
-        if (ok) ok = mbar_wait(smem_u32(&pv_done), static_cast<uint32_t>(n_tiles - 1) & 1u, status, 17);
+        if (ok) ok = mbar_wait(smem_u32(&pv_done[hh]), static_cast<uint32_t>(n_tiles - 1) & 1u, status, 17);
         tc_fence_after();
         if (ok) {
             // tcgen05.ld is a warp-wide instruction: rows past the portion's end take part and store nothing
@@ -339,24 +373,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfl
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base_slot, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base_slot, TMEM_COLS);
 }
 
-template <int HD>
+template <int HD, int HEADS>
 int launch_attn(const CUtensorMap* map_q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out,
                 const int32_t* block_table, int table_width, const int32_t* q_start, const int32_t* q_len, const int32_t* ctx_len,
                 int num_seqs, int max_tiles, int nq, int nkv, int page_shift, float scale, int window, int* status,
                 cudaStream_t stream) {
-    constexpr int smem = (HD / 64) * (kQRows * 128 + 4 * kKeys * 128) + 1024;      // Q, two key tiles, two value tiles
+    constexpr int stages = HEADS == 1 ? 2 : 4;
+    constexpr int smem = (HD / 64) * (HEADS * kQRows * 128 + 2 * stages * kKeys * 128) + 1024;      // Q tiles, key ring, value ring
     static bool configured = false;
-    auto kernel = attn_prefill_tc_kernel<HD>;
+    auto kernel = attn_prefill_tc_kernel<HD, HEADS>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(max_tiles, nq), dim3(kAttnThreads), smem, stream, *map_q, k_pages, v_pages, out, block_table,
-                   table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift, scale * 1.4426950408889634f, window, status);
+    stride::launch(kernel, dim3(nq / HEADS, max_tiles), dim3(HEADS == 1 ? 256 : 512), smem, stream, *map_q, k_pages, v_pages, out,
+                   block_table, table_width, q_start, q_len, ctx_len, num_seqs, nq, nkv, page_shift, scale * 1.4426950408889634f,
+                   window, status);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -364,6 +400,15 @@ int launch_attn(const CUtensorMap* map_q, const __nv_bfloat16* k_pages, const __
 }  // namespace stride
 
 using namespace stride;
+
+// STRIDE_ATTN_PAIR_HEADS=0 keeps one head per CTA (for comparisons).
+static bool pair_heads() {
+    static const bool on = [] {
+        const char* e = getenv("STRIDE_ATTN_PAIR_HEADS");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 // Attention for the first `num_seqs` requests of the step, which own the first `tokens` rows of
 // the flat batch. q: [tokens, q_stride] bf16 (head h at columns h*hd); out: [tokens, nq*hd];
@@ -389,12 +434,16 @@ extern "C" int stride_paged_prefill_attention_tc(const void* q, int q_stride, vo
     const CUtensorMap* map_q = tc::cached_map(q, tokens, q_stride, q_stride, tc::kQRows);
     if (!map_q) return STRIDE_UNSUPPORTED;
     const int max_tiles = (tokens + tc::kQRows - 1) / tc::kQRows + num_seqs;
+    if (max_tiles > 65535) return STRIDE_UNSUPPORTED;
     auto op = static_cast<__nv_bfloat16*>(out);
     auto kp = static_cast<const __nv_bfloat16*>(k_pages);
     auto vp = static_cast<const __nv_bfloat16*>(v_pages);
-    if (hd == 64)
-        return tc::launch_attn<64>(map_q, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq,
-                                   nkv, page_shift, scale, window, status, stream);
-    return tc::launch_attn<128>(map_q, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq, nkv,
-                                page_shift, scale, window, status, stream);
+    // Two heads of a key head per CTA share every key and value tile they load; with an odd group one head per CTA.
+    const bool pair = (nq / nkv) % 2 == 0 && pair_heads();
+#define STRIDE_ATTN_LAUNCH(HD_, HEADS_)                                                                                          \
+    tc::launch_attn<HD_, HEADS_>(map_q, kp, vp, op, block_table, table_width, q_start, q_len, ctx_len, num_seqs, max_tiles, nq, \
+                                 nkv, page_shift, scale, window, status, stream)
+    if (hd == 64) return pair ? STRIDE_ATTN_LAUNCH(64, 2) : STRIDE_ATTN_LAUNCH(64, 1);
+    return pair ? STRIDE_ATTN_LAUNCH(128, 2) : STRIDE_ATTN_LAUNCH(128, 1);
+#undef STRIDE_ATTN_LAUNCH
 }

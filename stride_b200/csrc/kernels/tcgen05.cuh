@@ -26,10 +26,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Returns false (and records `code`) when the phase did not complete in time.
+// Returns false (and records `code`) when the phase did not complete in time. The loop does nothing but
+// try_wait (which itself suspends the thread for a while); every 64th turn it looks at the clock, and gives
+// up when the limit has passed or, once it has waited 50 us, when another wait has already recorded a
+// time-out (so that a kernel that has gone wrong drains quickly).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    const long long start = clock64();
-    while (true) {
+    long long start = 0;
+    for (uint32_t turn = 1;; ++turn) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -39,10 +42,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) return true;
-        if (*reinterpret_cast<volatile int*>(status) != 0) return false;       // another wait has already given up: drain quickly
-        if (clock64() - start > kWaitCycles) {
-            atomicCAS(status, 0, code);
-            return false;
+        if ((turn & 63u) == 0) {
+            const long long now = clock64();
+            if (start == 0) start = now;
+            const long long waited = now - start;
+            if (waited > kWaitCycles) {
+                atomicCAS(status, 0, code);
+                return false;
+            }
+            if (waited > 100000 && *reinterpret_cast<volatile int*>(status) != 0) return false;
         }
     }
 }
