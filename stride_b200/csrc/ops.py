@@ -177,7 +177,7 @@ def silu_mul(inp, out, block: int | None = None) -> None:
 # as the reference's engine does. STRIDE_B200_TC_GEMM=0 switches the kernel off.
 import os as _os
 
-TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else 16
+TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else int(_os.environ.get("STRIDE_TC_MAX_TOKENS", "16"))
 # ... and only for weight matrices with at least this many 128-row tiles: with fewer, the K range has to be
 # split over several CTAs and the partial-tile round trip makes the kernel slower than the library's inside
 # the decode step (measured: QKV and down lose 3-4 us each, gate/up and the head gain). STRIDE_TC_MIN_TILES=0
