@@ -49,6 +49,7 @@ class PagedAttention(Mixer):
             d[b["q"]] = TensorDecl((self.q_dim,), "vector")
             d[b["k"]] = TensorDecl((self.kv_dim,), "vector")
             d[b["v"]] = TensorDecl((self.kv_dim,), "vector")
+        d.update(self.position.declare())          # a position encoding may have tensors of its own
         return d
 
     def bind(self, weights):
@@ -57,6 +58,7 @@ class PagedAttention(Mixer):
         self.w_o = weights[w["o"]]
         if self.spec.bias:
             self.bias = torch.cat([weights[b["q"]], weights[b["k"]], weights[b["v"]]]).contiguous()
+        self.position.bind(weights)
 
     def named_tensors(self):
         w, b = self._names()
@@ -64,6 +66,7 @@ class PagedAttention(Mixer):
         out = {w["q"]: self.w_qkv[:q], w["k"]: self.w_qkv[q:k], w["v"]: self.w_qkv[k:], w["o"]: self.w_o}
         if self.bias is not None:
             out.update({b["q"]: self.bias[:q], b["k"]: self.bias[q:k], b["v"]: self.bias[k:]})
+        out.update(self.position.named_tensors())
         return out
 
     # ------------------------------------------------------------------- cache

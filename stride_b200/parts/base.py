@@ -88,8 +88,11 @@ class Part:
 
 
 class Norm(Part):
-    weight: torch.Tensor
-    eps: float
+    def apply(self, residual, pending, out, rows=None) -> None:
+        """``x = residual + pending`` in float32 (``pending`` may be None), ``out = norm(x)``. Without ``rows``
+        every row is produced and x is written back into ``residual`` (float32 [tokens, hidden]); with ``rows``
+        (int32 indices) only those rows are produced, into ``out[i]``, and ``residual`` stays as it is."""
+        raise NotImplementedError
 
 
 class PositionEncoding(Part):

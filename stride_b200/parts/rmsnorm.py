@@ -3,6 +3,7 @@ multiplying after the normalisation (python/stride_worker/layers.py:24-35)."""
 
 from __future__ import annotations
 
+from ..csrc import ops
 from .base import Norm, TensorDecl, register_part
 
 
@@ -22,6 +23,9 @@ class RMSNorm(Norm):
 
     def named_tensors(self):
         return {self._name: self.weight}
+
+    def apply(self, residual, pending, out, rows=None):
+        ops.add_rmsnorm(residual, pending, self.weight, out, self.eps, rows=rows)      # sum, write-back and norm in one kernel
 
 
 register_part("norm", "rmsnorm", RMSNorm)

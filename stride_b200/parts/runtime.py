@@ -66,8 +66,8 @@ class Runtime:
 class ResidualStream:
     """The residual stream of one step: a float32 [tokens, hidden] tensor plus at
     most one pending delta. ``add`` defers the sum so that the next ``normed``
-    fuses it with the norm: x = residual + delta in float32, written back, and
-    rmsnorm(x) * w out, in one kernel."""
+    can fuse it with the norm (``Norm.apply``): x = residual + delta in float32,
+    written back, and norm(x) out, in one kernel for RMSNorm."""
 
     def __init__(self, runtime: Runtime, tokens: int, hidden: int):
         self.rt = runtime
@@ -82,15 +82,15 @@ class ResidualStream:
         self._pending = delta
 
     def normed(self, norm, rows=None, tag: str = "normed"):
-        """rmsnorm(residual + pending) * weight. With ``rows`` (int32 indices) only
-        those rows are produced and the residual is left as it is."""
+        """norm(residual + pending). With ``rows`` (int32 indices) only those rows
+        are produced and the residual is left as it is."""
         if rows is None:
             out = self.rt.buffer(tag, self.tokens, self.hidden)
-            ops.add_rmsnorm(self.residual, self._pending, norm.weight, out, norm.eps)
+            norm.apply(self.residual, self._pending, out)
             self._pending = None
         else:
             out = self.rt.buffer(tag + "_rows", rows.shape[0], self.hidden, row_kind="rows")
-            ops.add_rmsnorm(self.residual, self._pending, norm.weight, out, norm.eps, rows=rows)
+            norm.apply(self.residual, self._pending, out, rows=rows)
         return out
 
     def materialize(self):
