@@ -53,7 +53,8 @@ _SIGNATURES = {
     "stride_paged_prefill_attention_tc": ("attention_prefill_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                                    c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
-    "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_longlong, c_void_p]),
 }
 
 
@@ -433,6 +434,26 @@ def paged_attention_prefill(q, q_stride: int, out, k_pages, v_pages, block_table
 
 
 # --------------------------------------------------------------------- sampling
+_sample_scratch: dict = {}
+
+
+def _sampling_scratch(device, rows: int, vocab: int):
+    """Zeroed int32 words for the segment results and tickets of ``sample_rows`` (it leaves the tickets zero)."""
+    f = _bound.get("stride_sample_scratch_words")
+    if f is None:
+        f = build.load_kernel_library("sampling").stride_sample_scratch_words
+        f.argtypes = [c_int, c_int]
+        f.restype = c_longlong
+        _bound["stride_sample_scratch_words"] = f
+    need = int(f(rows, vocab))
+    st = _sample_scratch.setdefault(device, {"buf": None, "retired": []})
+    if st["buf"] is None or st["buf"].numel() < need:
+        if st["buf"] is not None:
+            st["retired"].append(st["buf"])          # a captured graph may still use it
+        st["buf"] = torch.zeros(max(need, 1 << 18), dtype=torch.int32, device=device)
+    return st["buf"]
+
+
 def sample_rows(logits, out, temperature=None, uniform=None, suppress=None) -> None:
     """Greedy (no ``temperature``, or 0) or temperature sampling per row."""
     rows, vocab = logits.shape
@@ -440,7 +461,8 @@ def sample_rows(logits, out, temperature=None, uniform=None, suppress=None) -> N
         raise KernelError("logits rows must be dense")
     if not logits.is_cuda:
         raise KernelError("logits must live on a CUDA device; stride_b200 has no CPU path")
+    scratch = _sampling_scratch(logits.device, rows, vocab)
     _check(_fn("stride_sample_rows")(logits.data_ptr(), rows, vocab, logits.stride(0),
                                      _opt(temperature, "temperature", torch.float32),
                                      _opt(uniform, "uniform", torch.float32), _opt(suppress, "suppress", torch.int32),
-                                     _dev(out, "out", torch.int32), _stream()), "sample_rows")
+                                     _dev(out, "out", torch.int32), scratch.data_ptr(), scratch.numel(), _stream()), "sample_rows")
