@@ -172,20 +172,19 @@ def silu_mul(inp, out, block: int | None = None) -> None:
 
 
 # ----------------------------------------------------------------------- matmul
-# Up to this many rows (tokens) the bfloat16 product runs on the package's own
-# tcgen05 kernel, which streams the weights once through a TMA ring with the
-# weight rows as the 128-row tile side; above it the library product is called,
-# as the reference's engine does. STRIDE_B200_TC_GEMM=0 switches the kernel off.
+# Up to this many rows (tokens: a decode step) the bfloat16 products run on the package's own kernels, which
+# stream the weights once; above it the library product is called, as the reference's engine does.
+# STRIDE_B200_TC_GEMM=0 switches both off, STRIDE_TC_MAX_TOKENS moves the limit (the tcgen05 kernel takes up to
+# 256 rows, the weight-streaming kernel 16; measured at 32 and 64 rows the library is level or faster).
 import os as _os
 
 TC_GEMM_MAX_TOKENS = 0 if _os.environ.get("STRIDE_B200_TC_GEMM", "1") == "0" else int(_os.environ.get("STRIDE_TC_MAX_TOKENS", "16"))
-# ... and only for weight matrices with at least this many 128-row tiles: with fewer, the K range has to be
-# split over several CTAs and the partial-tile round trip makes the kernel slower than the library's inside
-# the decode step (measured: QKV and down lose 3-4 us each, gate/up and the head gain). STRIDE_TC_MIN_TILES=0
-# sends every product of up to TC_GEMM_MAX_TOKENS rows to the kernel.
+# The tcgen05 kernel (TMA ring, weight rows as the 128-row tile side) takes the weight matrices with at least this
+# many 128-row tiles (gate/up, the head): with fewer, K has to be split over several CTAs and the partial tiles go
+# through global memory. STRIDE_TC_MIN_TILES=0 sends every product to it.
 TC_GEMM_MIN_TILES = int(_os.environ.get("STRIDE_TC_MIN_TILES", "100"))
-# Smaller matrices at up to TC_GEMM_MAX_TOKENS rows go to the weight-streaming kernel, which needs no split of K
-# across CTAs. STRIDE_B200_STREAM_GEMM=0 sends them to the library product instead.
+# The smaller matrices (QKV, O, down) go to the weight-streaming kernel, which gives a CTA 16 rows and all of K.
+# STRIDE_B200_STREAM_GEMM=0 sends them to the library product instead.
 STREAM_GEMM = _os.environ.get("STRIDE_B200_STREAM_GEMM", "1") != "0"
 _TC_TICKETS = 8192
 _tc_state: dict = {}

@@ -54,4 +54,6 @@ def main(reference_python: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/python")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the reference's python/ folder>")
+    main(sys.argv[1])
