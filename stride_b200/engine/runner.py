@@ -72,7 +72,7 @@ class ModelRunner:
         self.steps = 0
         self.graph_replays = 0
         self.last_h2d_bytes = 0
-        self.launches_per_graph: dict[int, int] = {}
+        self.launches_per_graph: dict = {}
         self.replayed_launches = 0      # own kernels run through graph replays
 
     # ------------------------------------------------------------------ public
@@ -92,6 +92,9 @@ class ModelRunner:
             raise ValueError("a request is longer than max_model_len")
         if self.cuda_graphs and batch.decode_only and batch.num_rows == batch.num_seqs:
             logits = self._step_graph(batch)
+            return logits.cpu() if to_host else logits
+        if self.cuda_graphs and batch.num_seqs == 1 and batch.num_tokens == self.token_capacity and batch.num_rows <= 1:
+            logits = self._step_full_portion(batch)
             return logits.cpu() if to_host else logits
         return self._step_eager(batch, to_host)
 
@@ -199,5 +202,30 @@ class ModelRunner:
         self.replayed_launches += self.launches_per_graph[b]
         return logits[:batch.num_rows]
 
+    def _step_full_portion(self, batch):
+        """One request's portion that fills the token budget (every step but the last of a long prompt cut into
+        portions, when nothing else is running): always the same launches, whatever the position, so it is
+        replayed from a graph too, one for the portions that want no logits and one for those that want a row."""
+        key = ("portion", batch.num_rows)
+        entry = self._graphs.get(key)
+        if entry is None:
+            self._pack(self._eager, batch)
+            ctx = self._context(self._eager, batch, batch.num_tokens, batch.num_rows)
+            self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.counters["launches"]
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            self.launches_per_graph[key] = ops.counters["launches"] - before
+            entry = (graph, logits)
+            self._graphs[key] = entry
+        graph, logits = entry
+        self._pack(self._eager, batch)
+        graph.replay()
+        self.graph_replays += 1
+        self.replayed_launches += self.launches_per_graph[key]
+        return logits[:batch.num_rows]
+
     def captured_buckets(self) -> list[int]:
-        return sorted({b for b, _cb in self._graphs})
+        return sorted({k[0] for k in self._graphs if k[0] != "portion"})

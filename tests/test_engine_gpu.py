@@ -96,6 +96,22 @@ def test_small_budgets_small_pools_and_resume_give_the_same_tokens(case):
         assert m["kv_blocks_live"] == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_alone_is_prefilled_in_full_portions_from_a_graph(case, dtype):
+    """One request whose prompt is several token budgets long: every portion but the last fills the budget and is
+    replayed from the graph captured for such portions; the tokens are the plain ones."""
+    from stride_b200 import SamplingParams
+    prompt = seeded_tokens(3 * 16 + 5, case["cfg"]["vocab_size"], 777)
+    engine = engine_for(case, dtype, max_batch_tokens=16, max_batch_seqs=4)
+    out = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    assert_greedy(case, dtype, prompt, out.tokens, "full portions from a graph")
+    assert ("portion", 0) in engine.runner._graphs, "no full portion went through the graph"
+    replays = engine.runner.graph_replays
+    again = engine.generate([prompt[:40] + prompt[:13]], SamplingParams(temperature=0.0, max_tokens=6))[0]       # other positions, same graph
+    assert_greedy(case, dtype, prompt[:40] + prompt[:13], again.tokens, "full portions from a graph, second request")
+    assert engine.runner.graph_replays > replays
+
+
 def test_stop_rules(case):
     from stride_b200 import SamplingParams
     prompt = case["prompts"][-1]

@@ -144,7 +144,7 @@ def test_decoding_across_context_buckets(case, monkeypatch):
     session = session_for(case, "bfloat16", steps, graphs=True)
     got = replay(session, steps)
     check(got, case["want"]["bfloat16"], "bfloat16", "decode across context buckets")
-    assert len({cb for _b, cb in session.runner._graphs}) >= 3, "the context never moved to another graph"
+    assert len({k[1] for k in session.runner._graphs if k[0] != "portion"}) >= 3, "the context never moved to another graph"
 
 
 def test_an_unknown_token_or_too_few_pages_is_an_error_not_a_wrong_result(case):
