@@ -1,40 +1,45 @@
 // out = x @ w^T in bfloat16 for a handful of tokens (decode steps): the product is bound by
 // reading the weights once, so the kernel is built around that stream and nothing else.
 //
-// A CTA owns 16 weight rows and all of K; its warps take interleaved batches of 32-column steps
-// of K. mma.sync.m16n8k16 does not care which physical column sits in which k slot as long as
-// both operands agree, so thread (g, t) of a quad fetches the eight consecutive columns
-// 8t..8t+7 of rows g and g+8 and the same eight columns of token g of x, as 16-byte pieces, and
-// feeds them to two products (columns 0-3, then 4-7): every thread consumes exactly the pieces
-// it fetched itself. The pieces travel by cp.async into a ring in shared memory that is private
-// to the thread (no barrier, only cp.async.wait_group), several batches ahead. Shared memory
-// rather than registers as the landing zone on purpose: plain loads in flight live in the L1
-// part of the SM's memory, and when this kernel shares an SM with kernels that have configured
-// it for shared memory (which programmatic dependent launch makes the normal case), almost no
-// L1 is left and a load-based stream starves; a ring in shared memory does not care.
-// With 16 rows per CTA even a 4096 x 4096 matrix gives 256 CTAs, all resident at once, so
-// nothing is split across CTAs and nothing is reduced through global memory: the warps of a CTA
-// add their partial sums in shared memory in warp order. The first batches of weights are
-// requested before the kernel waits for its predecessor (the weights do not depend on it).
+// A CTA owns a run of weight rows (MT tiles of 16) and all of K; its warps take interleaved
+// batches of 32-column steps of K. mma.sync.m16n8k16 does not care which physical column sits
+// in which k slot as long as both operands agree, so thread (g, t) of a quad fetches the eight
+// consecutive columns 8t..8t+7 of rows g and g+8 of each tile and the same eight columns of
+// token g of x, as 16-byte pieces, and feeds them to two products (columns 0-3, then 4-7):
+// every thread consumes exactly the pieces it fetched itself. The pieces travel by cp.async
+// into a ring in shared memory that is private to the thread (no barrier, only
+// cp.async.wait_group), several batches ahead. Shared memory rather than registers as the
+// landing zone on purpose: plain loads in flight live in the L1 part of the SM's memory, and
+// when this kernel shares an SM with kernels that have configured it for shared memory (which
+// programmatic dependent launch makes the normal case), almost no L1 is left and a load-based
+// stream starves; a ring in shared memory does not care.
+// The rows are dealt out so that every SM gets one CTA with the same number of rows (28 of a
+// 4096-row matrix on 148 SMs): with whole 16-row tiles some SMs would stream twice as much as
+// others, and the kernel is as slow as its busiest SM. Nothing is split across CTAs and nothing
+// is reduced through global memory: the warps of a CTA add their partial sums in shared memory
+// in warp order. The first batches of weights are requested before the kernel waits for its
+// predecessor (the weights do not depend on it).
 #include "common.cuh"
 #include "mma.cuh"
 
 namespace stride {
 namespace stream_gemm {
 
-constexpr int kRows = 16;        // weight rows per CTA
 constexpr int kStepCols = 32;    // columns of K per warp step (a quad's four 16-byte pieces)
 constexpr int kUnroll = 2;       // steps per batch (one cp.async group)
+constexpr int kMaxTiles = 4;     // 16-row tiles per CTA at most
 
 __device__ __forceinline__ void cp_async_16_or_zero(void* smem, const void* gmem, bool valid) {
     const int bytes = valid ? 16 : 0;        // 0 source bytes: the 16 destination bytes are filled with zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem)), "l"(gmem), "r"(bytes));
 }
 
-template <int NT>
-struct Ring {
-    static constexpr int kStages = NT == 1 ? 4 : 3;      // 96 KB of ring per 256-thread CTA either way (deeper or shallower rings measured the same)
-};
+// Ring depth in batches: what fits into about 200 KB for 256 threads, four at most (deeper measured the same).
+__host__ __device__ constexpr int ring_stages(int nt, int mt, int warps) {
+    const int per_stage = kUnroll * (2 * mt + nt) * warps * 32 * 16;
+    const int fit = (200 * 1024) / per_stage;
+    return fit > 4 ? 4 : (fit < 2 ? 2 : fit);
+}
 
 // What the projection of queries, keys and values does with its result instead of storing it (MODE 2): bias,
 // rotation of queries and keys by the token's position (pairs (i, i + hd/2), float32 tables
@@ -51,31 +56,44 @@ struct QkvEpilogue {
     int nq, nkv, hd, page_size, rotate;
 };
 
-// NT: token tiles of eight. MODE 0: bfloat16 output, 1: float32 output, 2: the QKV projection with QkvEpilogue:
-// a CTA then owns eight rotation pairs of one head, rows p..p+7 and p + hd/2..p + hd/2 + 7, so that both
-// halves of a pair meet in its epilogue.
-template <int NT, int WARPS, int MODE>
+// NT: token tiles of eight, MT: row tiles of 16 per CTA. MODE 0: bfloat16 output, 1: float32 output; the CTA owns
+// rows [blockIdx.x * per_cta, + per_cta). MODE 2: the QKV projection with QkvEpilogue; the CTA owns per_cta rotation
+// pairs (pair p of head h is rows h * hd + p and h * hd + p + hd/2), eight per tile, rows 0-7 of the tile holding
+// the pairs' first halves and rows 8-15 their second halves, so that both halves of a pair meet in its epilogue.
+template <int NT, int MT, int WARPS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int m, int n,
-                   int k, const QkvEpilogue qkv) {
-    constexpr int STAGES = Ring<NT>::kStages;
+                   int k, int per_cta, const QkvEpilogue qkv) {
+    constexpr int STAGES = ring_stages(NT, MT, WARPS);
     constexpr int THREADS = WARPS * 32;
-    constexpr int PIECES = 2 + NT;           // per step: rows g and g + 8 of the weights, then one piece of x per token tile
+    constexpr int PIECES = 2 * MT + NT;      // per step: rows g and g + 8 of every tile, then one piece of x per token tile
     extern __shared__ __align__(16) uint4 ring[];        // [STAGES][kUnroll][PIECES][THREADS]
-    __shared__ float red[WARPS][NT][kRows][8];
+    __shared__ float red[WARPS][MT][NT][16][8];
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.x * kRows;
-    int row_lo = r0, row_hi = r0 + 8;                      // first weight row of fragment rows 0-7 and of rows 8-15
-    if (MODE == 2) {
-        const int per_head = qkv.hd / kRows;               // CTAs per head
-        const int head = blockIdx.x / per_head;
-        row_lo = head * qkv.hd + (blockIdx.x - head * per_head) * 8;
-        row_hi = row_lo + qkv.hd / 2;
+    const int half = qkv.hd / 2;
+    const int units = MODE == 2 ? n / 2 : n;              // rows, or rotation pairs
+    const int first = blockIdx.x * per_cta, last = min(first + per_cta, units);       // this CTA's rows or pairs
+    // the weight row behind fragment row g (lo) and g + 8 (hi) of tile mt, or -1
+    const __nv_bfloat16* w_lo[MT];
+    const __nv_bfloat16* w_hi[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int lo = -1, hi = -1;
+        if (MODE == 2) {
+            const int pair = first + mt * 8 + g;
+            if (pair < last) {
+                lo = (pair / half) * qkv.hd + pair % half;
+                hi = lo + half;
+            }
+        } else {
+            lo = first + mt * 16 + g < last ? first + mt * 16 + g : -1;
+            hi = first + mt * 16 + 8 + g < last ? first + mt * 16 + 8 + g : -1;
+        }
+        w_lo[mt] = lo >= 0 ? w + static_cast<size_t>(lo) * k + 8 * t : nullptr;
+        w_hi[mt] = hi >= 0 ? w + static_cast<size_t>(hi) * k + 8 * t : nullptr;
     }
-    const __nv_bfloat16* w_lo = w + static_cast<size_t>(min(row_lo + g, n - 1)) * k + 8 * t;
-    const __nv_bfloat16* w_hi = w + static_cast<size_t>(min(row_hi + g, n - 1)) * k + 8 * t;
     const int steps = (k + kStepCols - 1) / kStepCols;
     // K is dealt out in batches of kUnroll consecutive steps, batch b to warp b % WARPS
     const int batches = (steps + kUnroll - 1) / kUnroll;
@@ -87,8 +105,11 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         for (int u = 0; u < kUnroll; ++u) {
             const int col = column(batch, u);
             const bool in = batch < my_batches && col + 8 * t < k;      // k % 8 == 0: a thread's eight columns are all inside or all outside
-            cp_async_16_or_zero(slot(batch, u, 0), w_lo + (in ? col : 0), in);
-            cp_async_16_or_zero(slot(batch, u, 1), w_hi + (in ? col : 0), in);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                cp_async_16_or_zero(slot(batch, u, 2 * mt), w_lo[mt] ? w_lo[mt] + (in ? col : 0) : w, in && w_lo[mt]);
+                cp_async_16_or_zero(slot(batch, u, 2 * mt + 1), w_hi[mt] ? w_hi[mt] + (in ? col : 0) : w, in && w_hi[mt]);
+            }
         }
     };
     auto request_x = [&](int batch) {
@@ -99,16 +120,18 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
             for (int nt = 0; nt < NT; ++nt) {
                 const int token = nt * 8 + g;
                 const bool in = batch < my_batches && col < k && token < m;
-                cp_async_16_or_zero(slot(batch, u, 2 + nt), x + (in ? static_cast<size_t>(token) * k + col : 0), in);
+                cp_async_16_or_zero(slot(batch, u, 2 * MT + nt), x + (in ? static_cast<size_t>(token) * k + col : 0), in);
             }
         }
     };
 
-    float acc[NT][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
 #pragma unroll
     for (int b = 0; b < STAGES - 1; ++b) request_weights(b);
@@ -121,13 +144,16 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
     for (int b = 0; b < my_batches; ++b) {
         cp_async_wait<STAGES - 2>();       // batch b has landed; the pieces are this thread's own, so no barrier
-        uint4 wl[kUnroll], wh[kUnroll], xv[kUnroll][NT];
+        uint4 wl[kUnroll][MT], wh[kUnroll][MT], xv[kUnroll][NT];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            wl[u] = *slot(b, u, 0);
-            wh[u] = *slot(b, u, 1);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xv[u][nt] = *slot(b, u, 2 + nt);
+            for (int mt = 0; mt < MT; ++mt) {
+                wl[u][mt] = *slot(b, u, 2 * mt);
+                wh[u][mt] = *slot(b, u, 2 * mt + 1);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) xv[u][nt] = *slot(b, u, 2 * MT + nt);
         }
         // the stage read in the iteration before this one is free again
         request_weights(b + STAGES - 1);
@@ -135,41 +161,46 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         cp_async_commit();
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const uint32_t f0[4] = {wl[u].x, wh[u].x, wl[u].y, wh[u].y};
-            const uint32_t f1[4] = {wl[u].z, wh[u].z, wl[u].w, wh[u].w};
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                mma_bf16_16816(acc[nt], f0, xv[u][nt].x, xv[u][nt].y);
-                mma_bf16_16816(acc[nt], f1, xv[u][nt].z, xv[u][nt].w);
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t f0[4] = {wl[u][mt].x, wh[u][mt].x, wl[u][mt].y, wh[u][mt].y};
+                const uint32_t f1[4] = {wl[u][mt].z, wh[u][mt].z, wl[u][mt].w, wh[u][mt].w};
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_bf16_16816(acc[mt][nt], f0, xv[u][nt].x, xv[u][nt].y);
+                    mma_bf16_16816(acc[mt][nt], f1, xv[u][nt].z, xv[u][nt].w);
+                }
             }
         }
     }
     cp_async_wait<0>();
 
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        red[warp][nt][g][2 * t] = acc[nt][0];
-        red[warp][nt][g][2 * t + 1] = acc[nt][1];
-        red[warp][nt][g + 8][2 * t] = acc[nt][2];
-        red[warp][nt][g + 8][2 * t + 1] = acc[nt][3];
-    }
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            red[warp][mt][nt][g][2 * t] = acc[mt][nt][0];
+            red[warp][mt][nt][g][2 * t + 1] = acc[mt][nt][1];
+            red[warp][mt][nt][g + 8][2 * t] = acc[mt][nt][2];
+            red[warp][mt][nt][g + 8][2 * t + 1] = acc[mt][nt][3];
+        }
     __syncthreads();
     if (MODE == 2) {
         // one thread per (token, pair): same arithmetic as rope_kv_write_kernel on the product rounded to bfloat16
-        const int head = row_lo / qkv.hd, i0 = row_lo - head * qkv.hd, half = qkv.hd / 2;
-        for (int i = threadIdx.x; i < NT * 8 * 8; i += THREADS) {
-            const int c = i & 7, token = i >> 3;
-            if (token >= m) continue;
-            const int nt = token >> 3, tk = token & 7;
+        for (int i = threadIdx.x; i < NT * 8 * MT * 8; i += THREADS) {
+            const int local = i % (MT * 8), token = i / (MT * 8);
+            const int pair = first + local;
+            if (token >= m || pair >= last) continue;
+            const int mt = local >> 3, c = local & 7, nt = token >> 3, tk = token & 7;
             float a = 0.f, b = 0.f;
 #pragma unroll
             for (int wp = 0; wp < WARPS; ++wp) {
-                a += red[wp][nt][c][tk];
-                b += red[wp][nt][c + 8][tk];
+                a += red[wp][mt][nt][c][tk];
+                b += red[wp][mt][nt][c + 8][tk];
             }
             a = __bfloat162float(__float2bfloat16_rn(a));
             b = __bfloat162float(__float2bfloat16_rn(b));
-            const int idx = i0 + c;                        // index of the pair's first half inside the head
+            const int head = pair / half, idx = pair - head * half;        // index of the pair's first half inside the head
             if (qkv.bias) {
                 a = __fadd_rn(a, qkv.bias[head * qkv.hd + idx]);
                 b = __fadd_rn(b, qkv.bias[head * qkv.hd + idx + half]);
@@ -186,11 +217,11 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
             if (head < qkv.nq) {
                 dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(token) * n + head * qkv.hd;
             } else {
-                const int slot = qkv.slot_mapping ? qkv.slot_mapping[token] : -1;
-                if (slot >= 0) {
+                const int slot_of_token = qkv.slot_mapping ? qkv.slot_mapping[token] : -1;
+                if (slot_of_token >= 0) {
                     const bool is_key = head < qkv.nq + qkv.nkv;
                     const int kvh = is_key ? head - qkv.nq : head - qkv.nq - qkv.nkv;
-                    const int page = slot / qkv.page_size, offset = slot - page * qkv.page_size;
+                    const int page = slot_of_token / qkv.page_size, offset = slot_of_token - page * qkv.page_size;
                     dst = (is_key ? qkv.k_pages : qkv.v_pages) +
                           ((static_cast<size_t>(page) * qkv.nkv + kvh) * qkv.page_size + offset) * qkv.hd;
                 }
@@ -202,42 +233,68 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         }
     } else {
         // one thread per (token, row): the warps' partial sums are added in warp order
-        for (int i = threadIdx.x; i < NT * 8 * kRows; i += THREADS) {
-            const int row = i & (kRows - 1), token = i / kRows;
-            const int nt = token >> 3, tk = token & 7;
+        for (int i = threadIdx.x; i < NT * 8 * MT * 16; i += THREADS) {
+            const int local = i % (MT * 16), token = i / (MT * 16);
+            const int row = first + local;
+            if (token >= m || row >= last) continue;
+            const int mt = local >> 4, r = local & 15, nt = token >> 3, tk = token & 7;
             float sum = 0.f;
 #pragma unroll
-            for (int wp = 0; wp < WARPS; ++wp) sum += red[wp][nt][row][tk];
-            if (token < m && r0 + row < n) {
-                const size_t at = static_cast<size_t>(token) * n + r0 + row;
-                if (MODE == 1) static_cast<float*>(out)[at] = sum;
-                else static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(sum);
-            }
+            for (int wp = 0; wp < WARPS; ++wp) sum += red[wp][mt][nt][r][tk];
+            const size_t at = static_cast<size_t>(token) * n + row;
+            if (MODE == 1) static_cast<float*>(out)[at] = sum;
+            else static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(sum);
         }
     }
 }
 
-template <int NT, int WARPS, int MODE>
-int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, const QkvEpilogue& qkv, cudaStream_t stream) {
-    constexpr int smem = Ring<NT>::kStages * kUnroll * (2 + NT) * WARPS * 32 * 16;
-    auto kernel = gemm_stream_kernel<NT, WARPS, MODE>;
+template <int NT, int MT, int WARPS, int MODE>
+int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, int per_cta, int ctas,
+                 const QkvEpilogue& qkv, cudaStream_t stream) {
+    constexpr int smem = ring_stages(NT, MT, WARPS) * kUnroll * (2 * MT + NT) * WARPS * 32 * 16;
+    auto kernel = gemm_stream_kernel<NT, MT, WARPS, MODE>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(static_cast<unsigned>((n + kRows - 1) / kRows)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, qkv);
+    stride::launch(kernel, dim3(static_cast<unsigned>(ctas)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, per_cta, qkv);
     return STRIDE_LAUNCH_STATUS();
 }
 
+inline int sm_count() {
+    static const int count = [] {
+        int device = 0, sms = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
+        return sms > 0 ? sms : 148;
+    }();
+    return count;
+}
+
+// Rows (MODE 2: rotation pairs) per CTA: one CTA per SM with equal shares when a CTA's kMaxTiles tiles can hold
+// such a share, else full CTAs of kMaxTiles tiles.
 template <int NT, int MODE>
 int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream,
                   const QkvEpilogue& qkv = QkvEpilogue{}) {
     const int batches = ((k + kStepCols - 1) / kStepCols + kUnroll - 1) / kUnroll;
-    if (batches >= 8 * 4) return launch_warps<NT, 8, MODE>(x, w, out, m, n, k, qkv, stream);
-    if (batches >= 4 * 4) return launch_warps<NT, 4, MODE>(x, w, out, m, n, k, qkv, stream);
-    return launch_warps<NT, 2, MODE>(x, w, out, m, n, k, qkv, stream);
+    const int units = MODE == 2 ? n / 2 : n, per_tile = MODE == 2 ? 8 : 16;
+    int per_cta = (units + sm_count() - 1) / sm_count();
+    if (per_cta > kMaxTiles * per_tile) per_cta = kMaxTiles * per_tile;
+    if (batches < 8 * 4) {        // a short K (small models): one tile per CTA and fewer warps
+        per_cta = per_tile;
+        const int ctas = (units + per_cta - 1) / per_cta;
+        if (batches >= 4 * 4) return launch_warps<NT, 1, 4, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+        return launch_warps<NT, 1, 2, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+    }
+    const int tiles = (per_cta + per_tile - 1) / per_tile;
+    const int ctas = (units + per_cta - 1) / per_cta;
+    switch (tiles) {
+        case 1: return launch_warps<NT, 1, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+        case 2: return launch_warps<NT, 2, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+        case 3: return launch_warps<NT, 3, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+        default: return launch_warps<NT, 4, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+    }
 }
 
 }  // namespace stream_gemm
