@@ -362,6 +362,26 @@ __global__ void embed_gather_vec_kernel(const int32_t* __restrict__ ids, const i
     }
 }
 
+// The second half of an RMS norm that was folded into the product before it (gemm_bf16_stream.cu, RowNorm): x~
+// holds residual * weight in bfloat16, `partials` [count][16] the sums of squares of the residual per producer CTA
+// and token. out = x~ * rsqrt(sum / width + eps). Only needed when what consumes the norm cannot apply the factor
+// itself.
+__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ xt, const float* __restrict__ partials, int count, float eps,
+                                  __nv_bfloat16* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float factor;
+    const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        for (int c = 0; c < count; ++c) total += partials[c * 16 + t];
+        factor = rsqrtf(total / static_cast<float>(width) + eps);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        out[static_cast<size_t>(t) * width + c] = __float2bfloat16_rn(__bfloat162float(xt[static_cast<size_t>(t) * width + c]) * factor);
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -501,6 +521,15 @@ int stride_silu_mul(const void* in, void* out, int tokens, int inter, int block,
         stride::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, block, total);
     else
         return STRIDE_BAD_ARGUMENT;
+    return STRIDE_LAUNCH_STATUS();
+}
+
+int stride_scale_rows(const void* xtilde, const float* partials, int count, float eps, void* out, int tokens, int width,
+                      cudaStream_t stream) {
+    if (tokens < 0 || tokens > 16 || width <= 0 || count <= 0 || partials == nullptr) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    stride::launch(scale_rows_kernel, dim3(tokens), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(xtilde), partials, count, eps,
+                   static_cast<__nv_bfloat16*>(out), width);
     return STRIDE_LAUNCH_STATUS();
 }
 

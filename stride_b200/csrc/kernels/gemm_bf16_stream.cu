@@ -56,19 +56,36 @@ struct QkvEpilogue {
     int nq, nkv, hd, page_size, rotate;
 };
 
-// NT: token tiles of eight, MT: row tiles of 16 per CTA. MODE 0: bfloat16 output, 1: float32 output; the CTA owns
+// An RMS norm taken apart and folded into the products around it. The product before the norm (MODE 3) adds its
+// result to the residual stream, writes x~ = residual * norm_weight in bfloat16 (without the 1/rms factor) and, per
+// CTA and token, the sum of squares of the residual values it produced. The product after the norm reads x~ as its
+// activations, adds the partial sums up in CTA order, and multiplies its accumulators by rsqrt(sum / width + eps):
+// W (x~ / rms) = (W x~) / rms, with the norm's statistics and scaling in float32 as before and no kernel of its own.
+struct RowNorm {
+    const float* in_partials;          // consumer: [in_count][16] sums of squares per producer CTA and token, or null
+    int in_count;
+    float inv_width, eps;
+    float* residual;                   // producer (MODE 3): [tokens, n] float32, updated in place
+    const float* norm_weight;          // producer: [n]
+    float* out_partials;               // producer: [gridDim.x][16]
+};
+
+// NT: token tiles of eight, MT: row tiles of 16 per CTA. MODE 0: bfloat16 output, 1: float32 output, 3: RowNorm
+// producer (out receives x~); the CTA owns
 // rows [blockIdx.x * per_cta, + per_cta). MODE 2: the QKV projection with QkvEpilogue; the CTA owns per_cta rotation
 // pairs (pair p of head h is rows h * hd + p and h * hd + p + hd/2), eight per tile, rows 0-7 of the tile holding
 // the pairs' first halves and rows 8-15 their second halves, so that both halves of a pair meet in its epilogue.
 template <int NT, int MT, int WARPS, int MODE>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int m, int n,
-                   int k, int per_cta, const QkvEpilogue qkv) {
+                   int k, int per_cta, const QkvEpilogue qkv, const RowNorm norm) {
     constexpr int STAGES = ring_stages(NT, MT, WARPS);
     constexpr int THREADS = WARPS * 32;
     constexpr int PIECES = 2 * MT + NT;      // per step: rows g and g + 8 of every tile, then one piece of x per token tile
     extern __shared__ __align__(16) uint4 ring[];        // [STAGES][kUnroll][PIECES][THREADS]
     __shared__ float red[WARPS][MT][NT][16][8];
+    __shared__ float rstd_s[16];                          // per token: 1/rms of the norm folded into this product (1 without one)
+    __shared__ float sq_s[MODE == 3 ? NT * 8 : 1][MODE == 3 ? MT * 16 : 1];
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -141,6 +158,15 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         request_x(b);
         cp_async_commit();      // group b: x of batch b (and, in group 0, the weights requested above)
     }
+    if (threadIdx.x < 16) {     // the folded norm's 1/rms per token, while the ring fills; read after the barrier below
+        float scale = 1.f;
+        if (norm.in_partials != nullptr) {
+            float total = 0.f;
+            for (int c = 0; c < norm.in_count; ++c) total += norm.in_partials[c * 16 + threadIdx.x];
+            scale = rsqrtf(total * norm.inv_width + norm.eps);
+        }
+        rstd_s[threadIdx.x] = scale;
+    }
 
     for (int b = 0; b < my_batches; ++b) {
         cp_async_wait<STAGES - 2>();       // batch b has landed; the pieces are this thread's own, so no barrier
@@ -198,8 +224,8 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                 a += red[wp][mt][nt][c][tk];
                 b += red[wp][mt][nt][c + 8][tk];
             }
-            a = __bfloat162float(__float2bfloat16_rn(a));
-            b = __bfloat162float(__float2bfloat16_rn(b));
+            a = __bfloat162float(__float2bfloat16_rn(a * rstd_s[token]));
+            b = __bfloat162float(__float2bfloat16_rn(b * rstd_s[token]));
             const int head = pair / half, idx = pair - head * half;        // index of the pair's first half inside the head
             if (qkv.bias) {
                 a = __fadd_rn(a, qkv.bias[head * qkv.hd + idx]);
@@ -241,16 +267,35 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
             float sum = 0.f;
 #pragma unroll
             for (int wp = 0; wp < WARPS; ++wp) sum += red[wp][mt][nt][r][tk];
+            sum *= rstd_s[token];
             const size_t at = static_cast<size_t>(token) * n + row;
-            if (MODE == 1) static_cast<float*>(out)[at] = sum;
-            else static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(sum);
+            if (MODE == 1) {
+                static_cast<float*>(out)[at] = sum;
+            } else if (MODE == 3) {
+                // as the unfused path: the product rounded to bfloat16, added to the stream in float32
+                const float r_new = __fadd_rn(norm.residual[at], __bfloat162float(__float2bfloat16_rn(sum)));
+                norm.residual[at] = r_new;
+                static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(__fmul_rn(r_new, norm.norm_weight[row]));
+                sq_s[token][local] = r_new * r_new;
+            } else {
+                static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(sum);
+            }
+        }
+        if (MODE == 3) {
+            __syncthreads();
+            if (threadIdx.x < 16) {     // this CTA's sum of squares per token, in row order
+                float total = 0.f;
+                if (static_cast<int>(threadIdx.x) < m)
+                    for (int r = 0; r < last - first; ++r) total += sq_s[threadIdx.x][r];
+                norm.out_partials[blockIdx.x * 16 + threadIdx.x] = total;
+            }
         }
     }
 }
 
 template <int NT, int MT, int WARPS, int MODE>
 int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, int per_cta, int ctas,
-                 const QkvEpilogue& qkv, cudaStream_t stream) {
+                 const QkvEpilogue& qkv, const RowNorm& norm, cudaStream_t stream) {
     constexpr int smem = ring_stages(NT, MT, WARPS) * kUnroll * (2 * MT + NT) * WARPS * 32 * 16;
     auto kernel = gemm_stream_kernel<NT, MT, WARPS, MODE>;
     static bool configured = false;
@@ -259,7 +304,7 @@ int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int 
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(static_cast<unsigned>(ctas)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, per_cta, qkv);
+    stride::launch(kernel, dim3(static_cast<unsigned>(ctas)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, per_cta, qkv, norm);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -272,28 +317,41 @@ inline int sm_count() {
     return count;
 }
 
-// Rows (MODE 2: rotation pairs) per CTA: one CTA per SM with equal shares when a CTA's kMaxTiles tiles can hold
-// such a share, else full CTAs of kMaxTiles tiles.
+// Rows (MODE 2: rotation pairs) per CTA and the number of CTAs: one CTA per SM with equal shares when a CTA's
+// kMaxTiles tiles can hold such a share, else full CTAs of kMaxTiles tiles; a short K (small models) gets one tile
+// per CTA and fewer warps.
+struct Shape {
+    int per_cta, ctas, tiles, warps;
+};
+inline Shape shape_for(int n, int k, int mode) {
+    const int batches = ((k + kStepCols - 1) / kStepCols + kUnroll - 1) / kUnroll;
+    const int units = mode == 2 ? n / 2 : n, per_tile = mode == 2 ? 8 : 16;
+    Shape s;
+    if (batches < 8 * 4) {
+        s.per_cta = per_tile;
+        s.tiles = 1;
+        s.warps = batches >= 4 * 4 ? 4 : 2;
+    } else {
+        s.per_cta = (units + sm_count() - 1) / sm_count();
+        if (s.per_cta > kMaxTiles * per_tile) s.per_cta = kMaxTiles * per_tile;
+        s.tiles = (s.per_cta + per_tile - 1) / per_tile;
+        s.warps = 8;
+    }
+    s.ctas = (units + s.per_cta - 1) / s.per_cta;
+    return s;
+}
+
 template <int NT, int MODE>
 int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream,
-                  const QkvEpilogue& qkv = QkvEpilogue{}) {
-    const int batches = ((k + kStepCols - 1) / kStepCols + kUnroll - 1) / kUnroll;
-    const int units = MODE == 2 ? n / 2 : n, per_tile = MODE == 2 ? 8 : 16;
-    int per_cta = (units + sm_count() - 1) / sm_count();
-    if (per_cta > kMaxTiles * per_tile) per_cta = kMaxTiles * per_tile;
-    if (batches < 8 * 4) {        // a short K (small models): one tile per CTA and fewer warps
-        per_cta = per_tile;
-        const int ctas = (units + per_cta - 1) / per_cta;
-        if (batches >= 4 * 4) return launch_warps<NT, 1, 4, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
-        return launch_warps<NT, 1, 2, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
-    }
-    const int tiles = (per_cta + per_tile - 1) / per_tile;
-    const int ctas = (units + per_cta - 1) / per_cta;
-    switch (tiles) {
-        case 1: return launch_warps<NT, 1, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
-        case 2: return launch_warps<NT, 2, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
-        case 3: return launch_warps<NT, 3, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
-        default: return launch_warps<NT, 4, 8, MODE>(x, w, out, m, n, k, per_cta, ctas, qkv, stream);
+                  const QkvEpilogue& qkv = QkvEpilogue{}, const RowNorm& norm = RowNorm{}) {
+    const Shape s = shape_for(n, k, MODE);
+    if (s.warps == 4) return launch_warps<NT, 1, 4, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+    if (s.warps == 2) return launch_warps<NT, 1, 2, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+    switch (s.tiles) {
+        case 1: return launch_warps<NT, 1, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+        case 2: return launch_warps<NT, 2, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+        case 3: return launch_warps<NT, 3, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+        default: return launch_warps<NT, 4, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
     }
 }
 
@@ -327,7 +385,8 @@ extern "C" int stride_gemm_stream_bf16(const void* x, const void* w, void* out, 
 extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* qkv_out, const float* bias, const int32_t* positions,
                                            const int32_t* slot_mapping, const float* cos_table, const float* sin_table,
                                            void* k_pages, void* v_pages, int tokens, int nq, int nkv, int hd, int page_size,
-                                           int k, int rotate, cudaStream_t stream) {
+                                           int k, int rotate, const float* norm_partials, int norm_count, float norm_eps,
+                                           cudaStream_t stream) {
     if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || k <= 0 || positions == nullptr) return STRIDE_BAD_ARGUMENT;
     if (tokens > 16 || hd % 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
@@ -336,6 +395,38 @@ extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* q
     auto xp = static_cast<const __nv_bfloat16*>(x);
     auto wp = static_cast<const __nv_bfloat16*>(w);
     const int n_out = (nq + 2 * nkv) * hd;
-    if (tokens <= 8) return stream_gemm::launch_stream<1, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e);
-    return stream_gemm::launch_stream<2, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e);
+    stream_gemm::RowNorm norm{};       // x may be the x~ of a folded norm: norm_partials [norm_count][16], width k
+    if (norm_partials != nullptr) {
+        if (norm_count <= 0) return STRIDE_BAD_ARGUMENT;
+        norm.in_partials = norm_partials;
+        norm.in_count = norm_count;
+        norm.inv_width = 1.f / static_cast<float>(k);
+        norm.eps = norm_eps;
+    }
+    if (tokens <= 8) return stream_gemm::launch_stream<1, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e, norm);
+    return stream_gemm::launch_stream<2, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e, norm);
+}
+
+// The product before an RMS norm, for at most 16 tokens: residual [tokens, n_out] float32 += bf16(x @ w^T),
+// xtilde [tokens, n_out] bf16 = residual * norm_weight, partials [ctas][16] = sums of squares of the new residual
+// per CTA and token; *ctas_out receives the number of CTAs (what the consumer has to add up). Returns -2 for
+// what it does not take, -1 if `partials_capacity` (floats) is too small.
+extern "C" int stride_gemm_stream_add_norm(const void* x, const void* w, void* xtilde, float* residual, const float* norm_weight,
+                                           float* partials, long long partials_capacity, int tokens, int n_out, int k,
+                                           int* ctas_out, cudaStream_t stream) {
+    if (tokens < 0 || n_out <= 0 || k <= 0 || residual == nullptr || norm_weight == nullptr || partials == nullptr || ctas_out == nullptr)
+        return STRIDE_BAD_ARGUMENT;
+    if (tokens > 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
+    const stream_gemm::Shape shape = stream_gemm::shape_for(n_out, k, 3);
+    if (partials_capacity < static_cast<long long>(shape.ctas) * 16) return STRIDE_BAD_ARGUMENT;
+    *ctas_out = shape.ctas;
+    if (tokens == 0) return 0;
+    stream_gemm::RowNorm norm{};
+    norm.residual = residual;
+    norm.norm_weight = norm_weight;
+    norm.out_partials = partials;
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    auto wp = static_cast<const __nv_bfloat16*>(w);
+    if (tokens <= 8) return stream_gemm::launch_stream<1, 3>(xp, wp, xtilde, tokens, n_out, k, stream, stream_gemm::QkvEpilogue{}, norm);
+    return stream_gemm::launch_stream<2, 3>(xp, wp, xtilde, tokens, n_out, k, stream, stream_gemm::QkvEpilogue{}, norm);
 }

@@ -52,7 +52,8 @@ template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out,
                     int ldo, int M, int N, int K, int k_blocks_per_split, float* __restrict__ partials,
-                    int* __restrict__ tickets, int* __restrict__ status) {
+                    int* __restrict__ tickets, int* __restrict__ status, const float* __restrict__ norm_partials, int norm_count,
+                    float norm_eps) {
     constexpr int A_BYTES = kBlockM * kBlockK * 2;
     constexpr int B_BYTES = BLOCK_N * kBlockK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -136,6 +137,13 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- epilogue: warps 2..5 own the lane quadrants 2, 3, 0, 1 of tensor memory
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                  // row of the tile this thread holds
+        float norm_part = 0.f;                             // GATED with a folded norm: this thread's share of a token's sum of squares
+        if constexpr (GATED) {
+            if (norm_partials != nullptr) {
+                pdl_wait();                                // the sums are written by the kernel before this one
+                for (int c = row >> 4; c < norm_count; c += 8) norm_part += norm_partials[c * 16 + (row & 15)];
+            }
+        }
         const bool ok = mbar_wait(smem_u32(&done_bar), 0, status, 3);
         tc_fence_after();
         pdl_wait();        // returns at once here (the producer passed it long ago); keeps this thread's stores ordered too
@@ -145,6 +153,21 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                   : nullptr;
         if constexpr (GATED) {
             static_assert(!GATED || (BLOCK_N == 16 && TRANSPOSED), "the gated epilogue is written for one 16-token column block");
+            // The activations may be the x~ of an RMS norm folded into the products around it (gemm_bf16_stream.cu,
+            // RowNorm): then the accumulators still lack the factor 1/rms of their token, which is formed here from
+            // the producer's sums of squares (norm_partials [norm_count][16], width K), eight threads per token,
+            // added in a fixed order.
+            float* fold = reinterpret_cast<float*>(smem) + 64 * 17;         // [8][16] partial sums, then [16] factors
+            {
+                fold[(row >> 4) * 16 + (row & 15)] = norm_part;      // summed while the products were still running
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (row < 16) {
+                    float all = 0.f;
+#pragma unroll
+                    for (int p8 = 0; p8 < 8; ++p8) all += fold[p8 * 16 + row];
+                    fold[128 + row] = norm_partials != nullptr ? rsqrtf(all / static_cast<float>(K) + norm_eps) : 1.f;
+                }
+            }
             float v[16];
             if (ok && num_kb > 0) {
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16), v);
@@ -160,6 +183,10 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int j = 0; j < 16; ++j) up_rows[row - 64][j] = v[j];
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps, on every path
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= fold[128 + j];
+            }
             if (ok && row < 64) {
                 const int col = m0 / 2 + row;                        // column of the inner activation
 #pragma unroll
@@ -168,7 +195,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (c < N) {
                         // as the unfused path: both products rounded to bfloat16, the activation in float32
                         const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
-                        const float u = __bfloat162float(__float2bfloat16_rn(up_rows[row][j]));
+                        const float u = __bfloat162float(__float2bfloat16_rn(up_rows[row][j] * fold[128 + j]));
                         out[static_cast<size_t>(c) * ldo + col] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
                     }
                 }
@@ -238,7 +265,8 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BLOCK_N, int STAGES, bool TRANSPOSED, typename OutT, bool GATED = false>
 int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ldo, int M, int N, int K, int splits,
-           float* partials, int* tickets, int* status, cudaStream_t stream) {
+           float* partials, int* tickets, int* status, cudaStream_t stream, const float* norm_partials = nullptr, int norm_count = 0,
+           float norm_eps = 0.f) {
     constexpr int smem = STAGES * (kBlockM * kBlockK * 2 + BLOCK_N * kBlockK * 2) + 1024;
     static bool configured = false;
     auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, TRANSPOSED, TRANSPOSED, OutT, GATED>;   // swapped use: A holds weights
@@ -250,7 +278,8 @@ int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ld
     const int k_blocks = (K + kBlockK - 1) / kBlockK;
     const int per_split = (k_blocks + splits - 1) / splits;
     dim3 grid((M + kBlockM - 1) / kBlockM, (N + BLOCK_N - 1) / BLOCK_N, splits);
-    stride::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, *map_a, *map_b, out, ldo, M, N, K, per_split, partials, tickets, status);
+    stride::launch(kernel, dim3(grid), dim3(kThreads), smem, stream, *map_a, *map_b, out, ldo, M, N, K, per_split, partials, tickets, status,
+                   norm_partials, norm_count, norm_eps);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -325,8 +354,10 @@ int stride_gemm_tc_skinny(const void* x, const void* w, void* out, int tokens, i
 // out = silu(x @ gate^T) * (x @ up^T) for at most 16 tokens. w: [2 * inner, k] bf16 with the rows of gate and up
 // alternating in blocks of 64 (gate 0-63, up 0-63, gate 64-127, ...); out: [tokens, inner] bf16. Returns -2 for
 // what it does not take (inner % 64 != 0, more than 16 tokens, sizes for which K would be split, unaligned
-// operands); the caller then runs the product and the activation separately.
-int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, int inner, int k, int* status, cudaStream_t stream) {
+// operands); the caller then runs the product and the activation separately. With norm_partials, x is the x~ of a
+// folded RMS norm (see the kernel) and the factor 1/rms per token is applied here.
+int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, int inner, int k, int* status,
+                         const float* norm_partials, int norm_count, float norm_eps, cudaStream_t stream) {
     if (tokens < 0 || inner <= 0 || k <= 0) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     if (status == nullptr) return STRIDE_BAD_ARGUMENT;
@@ -336,7 +367,7 @@ int stride_gemm_tc_gated(const void* x, const void* w, void* out, int tokens, in
     const CUtensorMap* map_b = tc::cached_map(x, tokens, k, k, 16);
     if (!map_a || !map_b) return STRIDE_UNSUPPORTED;
     return tc::launch<16, 6, true, __nv_bfloat16, true>(map_a, map_b, static_cast<__nv_bfloat16*>(out), inner, 2 * inner, tokens, k, 1,
-                                                        nullptr, nullptr, status, stream);
+                                                        nullptr, nullptr, status, stream, norm_partials, norm_count, norm_eps);
 }
 
 }  // extern "C"

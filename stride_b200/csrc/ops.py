@@ -34,7 +34,8 @@ _SIGNATURES = {
     "stride_rope_kv_write": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
-    "stride_gemm_tc_gated": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "stride_gemm_tc_gated": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+                                              c_void_p]),
     "stride_gemm_nt_f32": ("gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_paged_attention_generic": ("attention_generic", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -43,7 +44,11 @@ _SIGNATURES = {
                                                c_void_p, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_gemm_stream_qkv_rope": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                         c_void_p, c_int, c_float, c_void_p]),
+    "stride_gemm_stream_add_norm": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                         c_int, c_int, c_int, c_void_p, c_void_p]),
+    "stride_scale_rows": ("elementwise", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
@@ -262,17 +267,69 @@ def linear_tc(x, weight, out) -> bool:
 GATED_BLOCK = 64      # rows of gate and up alternate in blocks of this many in a weight laid out for ``linear_gated_tc``
 
 
-def linear_gated_tc(x, weight, out) -> bool:
+FOLD_NORMS = _os.environ.get("STRIDE_B200_FOLD_NORMS", "1") != "0"
+
+
+class FoldedNorm:
+    """The output of an RMS norm whose two halves were folded into the products around it: ``xt`` holds
+    ``residual * weight`` in bfloat16 (no 1/rms yet), ``partials`` [count, 16] the sums of squares of the
+    residual per producer CTA and token. A product that takes it applies ``rsqrt(sum / width + eps)`` to its
+    accumulators; anything else asks for ``tensor()``, which runs the small kernel that finishes the norm."""
+
+    def __init__(self, xt, partials, count: int, eps: float, make_buffer):
+        self.xt, self.partials, self.count, self.eps = xt, partials, int(count), float(eps)
+        self.shape, self.dtype, self.device = xt.shape, xt.dtype, xt.device
+        self._make_buffer = make_buffer
+        self._tensor = None
+
+    def tensor(self):
+        if self._tensor is None:
+            out = self._make_buffer()
+            _check(_fn("stride_scale_rows")(self.xt.data_ptr(), self.partials.data_ptr(), self.count, self.eps, out.data_ptr(),
+                                            self.shape[0], self.shape[1], _stream()), "scale_rows")
+            self._tensor = out
+        return self._tensor
+
+
+def _fold_args(folded):
+    if folded is None:
+        return None, 0, 0.0
+    return folded.partials.data_ptr(), folded.count, folded.eps
+
+
+def linear_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
+    """The product before an RMS norm, for at most 16 rows: ``residual += bf16(x @ weight.T)`` (float32),
+    ``xt = residual * norm_weight`` in bfloat16, ``partials[cta, token]`` the sums of squares. Returns the number
+    of producer CTAs (what a consumer has to add up), or 0 when the kernel does not take the sizes."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (FOLD_NORMS and STREAM_GEMM) or m > TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16 or residual.shape != (m, n):
+        return 0
+    count = c_int(0)
+    code = _fn("stride_gemm_stream_add_norm")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
+                                              _dev(xt, "xt", torch.bfloat16), _dev(residual, "residual", torch.float32),
+                                              _dev(norm_weight, "norm_weight", torch.float32), _dev(partials, "partials", torch.float32),
+                                              partials.numel(), m, n, k, ctypes.byref(count), _stream())
+    if code == -2:
+        return 0
+    _check(code, "gemm_stream_add_norm")
+    return count.value
+
+
+def linear_gated_tc(x, weight, out, folded=None) -> bool:
     """``out = silu(x @ gate.T) * (x @ up.T)`` in one tcgen05 kernel for at most 16 rows of ``x``; ``weight`` is
-    [2 * inter, k] with gate and up rows alternating in blocks of ``GATED_BLOCK``. Returns False when the kernel
-    does not take the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
+    [2 * inter, k] with gate and up rows alternating in blocks of ``GATED_BLOCK``. With ``folded`` (a FoldedNorm
+    whose ``xt`` is ``x``) the kernel applies the norm's 1/rms itself. Returns False when the kernel does not take
+    the sizes (the caller then runs the product and ``silu_mul`` with the same block)."""
     m, k = x.shape
     inter = weight.shape[0] // 2
     if m > TC_GEMM_MAX_TOKENS or out.shape != (m, inter):
         return False
     st = _tc_buffers(x.device, 0)
+    partials, count, eps = _fold_args(folded)
     code = _fn("stride_gemm_tc_gated")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
-                                       _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), _stream())
+                                       _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), partials, count, eps,
+                                       _stream())
     if code == -2:
         return False
     _check(code, "gemm_tc_gated")
@@ -293,19 +350,21 @@ def linear_stream(x, weight, out) -> bool:
 
 
 def linear_qkv_rope(x, weight, qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages, nq: int, nkv: int, hd: int,
-                    page_size: int, rotate: bool) -> bool:
+                    page_size: int, rotate: bool, folded=None) -> bool:
     """The projection of queries, keys and values with ``rope_kv_write`` in its epilogue, for at most 16 rows of
     ``x``: afterwards ``qkv`` holds the rotated queries (its key and value columns are not written) and the cache
-    the rotated keys and the values. Returns False when the kernel does not take the sizes; the caller then runs
-    ``linear`` and ``rope_kv_write``."""
+    the rotated keys and the values. With ``folded`` (a FoldedNorm whose ``xt`` is ``x``) the kernel applies the
+    norm's 1/rms itself. Returns False when the kernel does not take the sizes; the caller then runs ``linear`` and
+    ``rope_kv_write``."""
     m, k = x.shape
     if not STREAM_GEMM or m > TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16 or qkv.shape != (m, (nq + 2 * nkv) * hd):
         return False
+    partials, count, eps = _fold_args(folded)
     code = _fn("stride_gemm_stream_qkv_rope")(
         _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(qkv, "qkv", torch.bfloat16),
         _opt(bias, "bias", torch.float32), _dev(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
         _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages", torch.bfloat16),
-        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), _stream())
+        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), partials, count, eps, _stream())
     if code == -2:
         return False
     _check(code, "gemm_stream_qkv_rope")

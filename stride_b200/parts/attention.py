@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import CacheRequest, Mixer, TensorDecl, build_part, register_part
+from .base import CacheRequest, Mixer, Projection, TensorDecl, build_part, register_part
 
 
 class PagedAttention(Mixer):
@@ -74,20 +74,28 @@ class PagedAttention(Mixer):
         return CacheRequest(self.nkv, self.hd, self.spec.window)
 
     # ----------------------------------------------------------------- forward
-    def forward(self, x, ctx, cache):
+    lazy_output = True
+    accepts_folded = True
+
+    def forward(self, x, ctx, cache, lazy_output: bool = False):
         tokens = x.shape[0]
         qkv = self.rt.buffer("qkv", tokens, self.qkv_dim)
-        if not self._project_and_rotate(x, qkv, ctx, cache, tokens):
+        folded = x if isinstance(x, ops.FoldedNorm) else None
+        if not self._project_and_rotate(folded.xt if folded else x, qkv, ctx, cache, tokens, folded):
+            if folded:
+                x = folded.tensor()
             ops.linear(x, self.w_qkv, qkv)
             self.position.encode_and_store(qkv, self.bias, ctx, cache, self.nq, self.nkv, self.hd)
         attn = self.rt.buffer("attn", tokens, self.q_dim)
         self._attend(qkv, attn, ctx, cache, tokens)
+        if lazy_output:
+            return Projection(attn, self.w_o)          # the residual stream runs it, with the sum and norm that follow if it can
         out = self.rt.buffer("mixer_out", tokens, self.hidden)
         ops.linear(attn, self.w_o, out)
         return out
 
 
-    def _project_and_rotate(self, x, qkv, ctx, cache, tokens) -> bool:
+    def _project_and_rotate(self, x, qkv, ctx, cache, tokens, folded=None) -> bool:
         """A decode step's projection with the position encoding and the cache write in its epilogue, when the
         position part says that what it does is the standard rotation. False: nothing was done."""
         if tokens > ops.TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16:
@@ -98,7 +106,7 @@ class PagedAttention(Mixer):
         cos, sin, rotate = tables
         slots = ctx.slot_mapping[cache.group][:tokens] if cache.writes else None
         return ops.linear_qkv_rope(x, self.w_qkv, qkv, self.bias, ctx.positions[:tokens], slots, cos, sin, cache.k_pages,
-                                   cache.v_pages, self.nq, self.nkv, self.hd, cache.page_size, rotate)
+                                   cache.v_pages, self.nq, self.nkv, self.hd, cache.page_size, rotate, folded)
 
     def _attend(self, qkv, attn, ctx, cache, tokens):
         table = ctx.block_table[cache.group]

@@ -87,7 +87,21 @@ class Part:
         return {}
 
 
+class Projection:
+    """A part's last matrix product, not yet run: ``x @ weight.T``. A mixer or feed-forward that sets
+    ``lazy_output`` may return one instead of a tensor when it is called with ``lazy_output=True``; the residual
+    stream then runs the product together with the sum and the norm that follow it, or plainly if it cannot."""
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+
+
 class Norm(Part):
+    def fold_inputs(self):
+        """Optional. ``(weight, eps)`` if the norm is ``x * rsqrt(mean(x^2) + eps) * weight`` with a float32
+        weight: the residual stream may then fold it into the products before and after it."""
+        return None
+
     def apply(self, residual, pending, out, rows=None) -> None:
         """``x = residual + pending`` in float32 (``pending`` may be None), ``out = norm(x)``. Without ``rows``
         every row is produced and x is written back into ``residual`` (float32 [tokens, hidden]); with ``rows``
@@ -107,6 +121,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True: ``forward`` takes ``lazy_output=True`` and may then return a Projection (its output product, not yet run).
+    lazy_output = False
+    # True: ``forward`` may be given an ``ops.FoldedNorm`` instead of a normed tensor (``.tensor()`` turns it into one).
+    accepts_folded = False
+
     def cache_request(self) -> Optional[CacheRequest]:
         return None
 
@@ -118,6 +137,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    lazy_output = False       # as for Mixer
+    accepts_folded = False
+
     def forward(self, x, ctx):
         raise NotImplementedError
 
@@ -130,4 +152,4 @@ class Layer(Part):
 
 
 __all__ = ["CATEGORIES", "register_part", "build_part", "registered_parts", "CacheRequest", "StateRequest", "Part", "Norm",
-           "PositionEncoding", "Mixer", "FeedForward", "Layer", "TensorDecl"]
+           "PositionEncoding", "Mixer", "FeedForward", "Layer", "TensorDecl", "Projection"]

@@ -35,8 +35,13 @@ class PreNormLayer(Layer):
         return d
 
     def forward(self, stream, ctx, cache):
-        stream.add(self.mixer.forward(stream.normed(self.mixer_norm), ctx, cache))
-        stream.add(self.feed_forward.forward(stream.normed(self.ffn_norm), ctx))
+        # A part that can, gets the norm folded into its first product and leaves its last product to the stream,
+        # which folds it into the next norm (decode steps in bfloat16; everything else runs part by part).
+        mixer, ffn = self.mixer, self.feed_forward
+        h = stream.normed(self.mixer_norm, fold_ok=mixer.accepts_folded)
+        stream.add(mixer.forward(h, ctx, cache, lazy_output=True) if mixer.lazy_output else mixer.forward(h, ctx, cache))
+        h = stream.normed(self.ffn_norm, fold_ok=ffn.accepts_folded)
+        stream.add(ffn.forward(h, ctx, lazy_output=True) if ffn.lazy_output else ffn.forward(h, ctx))
 
 
 register_part("layer", "pre_norm", PreNormLayer)

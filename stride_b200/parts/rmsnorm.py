@@ -24,6 +24,9 @@ class RMSNorm(Norm):
     def named_tensors(self):
         return {self._name: self.weight}
 
+    def fold_inputs(self):
+        return self.weight, self.eps
+
     def apply(self, residual, pending, out, rows=None):
         ops.add_rmsnorm(residual, pending, self.weight, out, self.eps, rows=rows)      # sum, write-back and norm in one kernel
 

@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from .base import Projection
 
 
 class Runtime:
@@ -77,25 +78,62 @@ class ResidualStream:
         self._pending = None
 
     def add(self, delta) -> None:
-        if self._pending is not None:
-            ops.add_residual(self.residual, self._pending)
+        """``delta``: a tensor, or a ``Projection`` (a product not yet run) that the next ``normed`` may fold."""
+        self._settle()
         self._pending = delta
 
-    def normed(self, norm, rows=None, tag: str = "normed"):
+    def _settle(self) -> None:
+        """Applies what is pending to the residual."""
+        if self._pending is not None:
+            ops.add_residual(self.residual, self._run(self._pending))
+            self._pending = None
+
+    def _run(self, pending):
+        """The pending delta as a tensor (runs a deferred product)."""
+        if isinstance(pending, Projection):
+            out = self.rt.buffer("projection_out", self.tokens, pending.weight.shape[0])
+            ops.linear(pending.x, pending.weight, out)
+            return out
+        return pending
+
+    def normed(self, norm, rows=None, tag: str = "normed", fold_ok: bool = False):
         """norm(residual + pending). With ``rows`` (int32 indices) only those rows
-        are produced and the residual is left as it is."""
+        are produced and the residual is left as it is. With ``fold_ok`` the caller
+        takes an ``ops.FoldedNorm`` too: when the pending delta is a deferred product
+        and the norm allows it, product, sum and the norm's statistics become one
+        kernel and the norm's scaling is left to the consumer."""
+        if rows is None and fold_ok and isinstance(self._pending, Projection):
+            folded = self._fold(norm, tag)
+            if folded is not None:
+                return folded
+        pending = None if self._pending is None else self._run(self._pending)
         if rows is None:
             out = self.rt.buffer(tag, self.tokens, self.hidden)
-            norm.apply(self.residual, self._pending, out)
+            norm.apply(self.residual, pending, out)
             self._pending = None
         else:
+            self._pending = pending
             out = self.rt.buffer(tag + "_rows", rows.shape[0], self.hidden, row_kind="rows")
-            norm.apply(self.residual, self._pending, out, rows=rows)
+            norm.apply(self.residual, pending, out, rows=rows)
         return out
+
+    def _fold(self, norm, tag):
+        inputs = norm.fold_inputs()
+        if inputs is None:
+            return None
+        weight, eps = inputs
+        p = self._pending
+        if p.weight.shape[0] != self.hidden:
+            return None
+        xt = self.rt.buffer(tag + "_folded", self.tokens, self.hidden)
+        partials = self.rt.scratch("norm_partials", 16 * 1024)
+        count = ops.linear_add_norm(p.x, p.weight, self.residual, weight, xt, partials)
+        if not count:
+            return None
+        self._pending = None
+        return ops.FoldedNorm(xt, partials, count, eps, lambda: self.rt.buffer(tag, self.tokens, self.hidden))
 
     def materialize(self):
         """The stream with every pending sum applied (float32)."""
-        if self._pending is not None:
-            ops.add_residual(self.residual, self._pending)
-            self._pending = None
+        self._settle()
         return self.residual

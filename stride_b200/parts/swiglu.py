@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, TensorDecl, register_part
+from .base import FeedForward, Projection, TensorDecl, register_part
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
@@ -51,13 +51,21 @@ class SwiGLU(FeedForward):
         blocks = self.w_gate_up.view(self.inter // self.block, 2, self.block, self.hidden)
         return {g: blocks[:, 0].reshape(self.inter, self.hidden), u: blocks[:, 1].reshape(self.inter, self.hidden), d: self.w_down}
 
-    def forward(self, x, ctx):
+    lazy_output = True
+    accepts_folded = True
+
+    def forward(self, x, ctx, lazy_output: bool = False):
         tokens = x.shape[0]
         act = self.rt.buffer("ffn_act", tokens, self.inter)
-        if not (self.block == ops.GATED_BLOCK and ops.linear_gated_tc(x, self.w_gate_up, act)):
+        folded = x if isinstance(x, ops.FoldedNorm) else None
+        if not (self.block == ops.GATED_BLOCK and ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded)):
+            if folded:
+                x = folded.tensor()
             gate_up = self.rt.buffer("gate_up", tokens, 2 * self.inter)
             ops.linear(x, self.w_gate_up, gate_up)
             ops.silu_mul(gate_up, act, self.block)
+        if lazy_output:
+            return Projection(act, self.w_down)        # the residual stream runs it, with the sum and norm that follow if it can
         out = self.rt.buffer("ffn_out", tokens, self.hidden)
         ops.linear(act, self.w_down, out)
         return out

@@ -508,6 +508,69 @@ def test_streaming_projection_with_rotation_and_cache_write(ops, tokens, nq, nkv
     assert float(k1.float().sub(3.0).abs().max()) > 0.0     # something was stored
 
 
+@pytest.mark.parametrize("tokens,hidden,k,inter", [(8, 4096, 4096, 14336), (3, 192, 512, 320), (16, 1024, 2048, 1024), (1, 4096, 14336, 14336)])
+def test_rms_norm_folded_into_the_products_around_it(ops, tokens, hidden, k, inter):
+    """product -> sum -> norm -> product as three kernels and as two: the product before the norm adds to the
+    residual and leaves x~ and sums of squares, the product after it applies 1/rms to its accumulators."""
+    from stride_b200.parts.swiglu import interleave_gate_up
+    g = torch.Generator().manual_seed(35)
+    x = dev(torch.randn(tokens, k, generator=g).bfloat16())
+    w = dev((torch.randn(hidden, k, generator=g) * 0.05).bfloat16())
+    residual0 = torch.randn(tokens, hidden, generator=g) * 3
+    norm_w = dev(1 + 0.1 * torch.randn(hidden, generator=g))
+    eps = 1e-5
+    # in steps: product, then sum and norm in one kernel
+    delta = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    ops.linear_stream(x, w, delta)
+    res_a = dev(residual0.clone())
+    normed = torch.empty_like(delta)
+    ops.add_rmsnorm(res_a, delta, norm_w, normed, eps)
+    # folded
+    res_b = dev(residual0.clone())
+    xt = torch.empty_like(delta)
+    partials = torch.full((16 * 1024,), float("nan"), device="cuda")
+    count = ops.linear_add_norm(x, w, res_b, norm_w, xt, partials)
+    assert count > 0, "the kernel refused sizes it should take"
+    torch.cuda.synchronize()
+    assert torch.equal(res_a, res_b), "the residual stream differs"
+    folded = ops.FoldedNorm(xt, partials, count, eps, lambda: torch.empty_like(delta))
+    close(folded.tensor(), normed.double(), torch.bfloat16)
+    want = res_a.double() * torch.rsqrt((res_a.double() ** 2).mean(-1, keepdim=True) + eps) * norm_w.double().cpu().to(res_a.device)
+    close(folded.tensor(), want, torch.bfloat16)
+    # the consumer applies 1/rms itself: gated feed-forward product
+    if inter % 64 == 0 and tokens <= 16:
+        gate = (torch.randn(inter, hidden, generator=g) * 0.05).bfloat16()
+        up = (torch.randn(inter, hidden, generator=g) * 0.05).bfloat16()
+        wgu = dev(interleave_gate_up(gate, up, ops.GATED_BLOCK))
+        plain_out = torch.empty(tokens, inter, dtype=torch.bfloat16, device="cuda")
+        fold_out = torch.empty_like(plain_out)
+        if ops.linear_gated_tc(normed, wgu, plain_out):
+            assert ops.linear_gated_tc(xt, wgu, fold_out, folded)
+            torch.cuda.synchronize()
+            assert ops.tc_status() == 0
+            close(fold_out, plain_out.double(), torch.bfloat16)
+    # ... and the projection of queries, keys and values
+    if hidden % 128 == 0:
+        nq, nkv, hd, page = hidden // 128, 1, 128, 16
+        heads = nq + 2 * nkv
+        wqkv = dev((torch.randn(heads * hd, hidden, generator=g) * 0.05).bfloat16())
+        positions = dev(torch.arange(tokens, dtype=torch.int32) * 3)
+        slots = dev(torch.arange(tokens, dtype=torch.int32))
+        inv = plain.rope_inv_freq(hd, 10000.0, None)
+        angles = torch.outer(torch.arange(64, dtype=torch.float32), inv)
+        cos, sin = dev(angles.cos()), dev(angles.sin())
+        results = []
+        for source, fold in ((normed, None), (xt, folded)):
+            k_pages = torch.zeros(2, nkv, page, hd, dtype=torch.bfloat16, device="cuda")
+            v_pages = torch.zeros_like(k_pages)
+            qkv = torch.zeros(tokens, heads * hd, dtype=torch.bfloat16, device="cuda")
+            assert ops.linear_qkv_rope(source, wqkv, qkv, None, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, True, fold)
+            torch.cuda.synchronize()
+            results.append((qkv[:, :nq * hd].clone(), k_pages, v_pages))
+        for a, b in zip(results[0], results[1]):
+            close(b, a.double(), torch.bfloat16, scale=float(results[0][0].double().abs().max()))
+
+
 def test_streaming_product_refuses_what_it_cannot_run(ops):
     w = torch.zeros(128, 100, dtype=torch.bfloat16, device="cuda")
     assert not ops.linear_stream(torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda"), w,
