@@ -85,6 +85,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     extern __shared__ __align__(16) uint4 ring[];        // [STAGES][kUnroll][PIECES][THREADS]
     __shared__ float red[WARPS][MT][NT][16][8];
     __shared__ float rstd_s[16];                          // per token: 1/rms of the norm folded into this product (1 without one)
+    __shared__ float share_s[WARPS * 2][16];              // its sums of squares, one share per 16 threads
     __shared__ float sq_s[MODE == 3 ? NT * 8 : 1][MODE == 3 ? MT * 16 : 1];
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,14 +159,34 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         request_x(b);
         cp_async_commit();      // group b: x of batch b (and, in group 0, the weights requested above)
     }
-    if (threadIdx.x < 16) {     // the folded norm's 1/rms per token, while the ring fills; read after the barrier below
-        float scale = 1.f;
+    // The folded norm's sums of squares, while the ring fills: every thread adds up a share of the producer CTAs for
+    // one token (loads first, then the sums, so that no load waits for another); the shares meet after the main loop.
+    constexpr int SHARES = THREADS / 16;
+    {
+        float share = 0.f;
         if (norm.in_partials != nullptr) {
-            float total = 0.f;
-            for (int c = 0; c < norm.in_count; ++c) total += norm.in_partials[c * 16 + threadIdx.x];
-            scale = rsqrtf(total * norm.inv_width + norm.eps);
+            const int token = threadIdx.x & 15, part = threadIdx.x >> 4;
+            for (int c0 = part; c0 < norm.in_count; c0 += SHARES * 4) {
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = c0 + j * SHARES < norm.in_count ? norm.in_partials[(c0 + j * SHARES) * 16 + token] : 0.f;
+                share += (v[0] + v[1]) + (v[2] + v[3]);
+            }
         }
-        rstd_s[threadIdx.x] = scale;
+        share_s[threadIdx.x >> 4][threadIdx.x & 15] = share;
+    }
+    // The producer's epilogue reads the residual and the norm's weight; ask for them now.
+    constexpr int ITEMS = (NT * 8 * MT * 16 + THREADS - 1) / THREADS;
+    float res_pre[MODE == 3 ? ITEMS : 1], w_pre[MODE == 3 ? ITEMS : 1];
+    if (MODE == 3) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int i = threadIdx.x + it * THREADS;
+            const int local = i % (MT * 16), token = i / (MT * 16), row = first + local;
+            const bool live = i < NT * 8 * MT * 16 && token < m && row < last;
+            res_pre[it] = live ? norm.residual[static_cast<size_t>(token) * n + row] : 0.f;
+            w_pre[it] = live ? norm.norm_weight[row] : 0.f;
+        }
     }
 
     for (int b = 0; b < my_batches; ++b) {
@@ -210,6 +231,17 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
             red[warp][mt][nt][g + 8][2 * t] = acc[mt][nt][2];
             red[warp][mt][nt][g + 8][2 * t + 1] = acc[mt][nt][3];
         }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        float scale = 1.f;
+        if (norm.in_partials != nullptr) {
+            float total = 0.f;
+#pragma unroll
+            for (int p = 0; p < SHARES; ++p) total += share_s[p][threadIdx.x];
+            scale = rsqrtf(total * norm.inv_width + norm.eps);
+        }
+        rstd_s[threadIdx.x] = scale;
+    }
     __syncthreads();
     if (MODE == 2) {
         // one thread per (token, pair): same arithmetic as rope_kv_write_kernel on the product rounded to bfloat16
@@ -259,10 +291,12 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         }
     } else {
         // one thread per (token, row): the warps' partial sums are added in warp order
-        for (int i = threadIdx.x; i < NT * 8 * MT * 16; i += THREADS) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+            const int i = threadIdx.x + it * THREADS;
             const int local = i % (MT * 16), token = i / (MT * 16);
             const int row = first + local;
-            if (token >= m || row >= last) continue;
+            if (i >= NT * 8 * MT * 16 || token >= m || row >= last) continue;
             const int mt = local >> 4, r = local & 15, nt = token >> 3, tk = token & 7;
             float sum = 0.f;
 #pragma unroll
@@ -273,9 +307,9 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                 static_cast<float*>(out)[at] = sum;
             } else if (MODE == 3) {
                 // as the unfused path: the product rounded to bfloat16, added to the stream in float32
-                const float r_new = __fadd_rn(norm.residual[at], __bfloat162float(__float2bfloat16_rn(sum)));
+                const float r_new = __fadd_rn(res_pre[MODE == 3 ? it : 0], __bfloat162float(__float2bfloat16_rn(sum)));
                 norm.residual[at] = r_new;
-                static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(__fmul_rn(r_new, norm.norm_weight[row]));
+                static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(__fmul_rn(r_new, w_pre[MODE == 3 ? it : 0]));
                 sq_s[token][local] = r_new * r_new;
             } else {
                 static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(sum);
