@@ -52,6 +52,9 @@ _SIGNATURES = {
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
+    "stride_paged_decode_attention_tma": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                               c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                                               c_int, c_float, c_int, c_int, c_void_p, c_void_p]),
     "stride_paged_prefill_attention": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                              c_int, c_float, c_int, c_void_p]),
@@ -446,12 +449,12 @@ def paged_attention_decode(q, q_stride: int, out, k_pages, v_pages, block_table,
     tokens = out.shape[0]
     if out.shape[1] != nq * hd:
         raise KernelError("attention output has the wrong width")
-    _check(_fn("stride_paged_decode_attention")(
+    _check(_fn("stride_paged_decode_attention_tma")(
         _dev(q, "q", torch.bfloat16), q_stride, _dev(out, "out", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
-        _dev(v_pages, "v_pages", torch.bfloat16), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
-        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(v_pages, "v_pages", torch.bfloat16), k_pages.shape[0], _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], _dev(seq_of_token, "seq_of_token", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(scratch, "scratch", torch.float32), scratch.numel(), tokens, nq, nkv, hd, page_size, float(scale), int(window),
-        int(max_context), _stream()), "paged_attention_decode")
+        int(max_context), _tc_buffers(q.device, 0)["status"].data_ptr(), _stream()), "paged_attention_decode")
 
 
 TC_ATTENTION = _os.environ.get("STRIDE_B200_TC_ATTENTION", "1") != "0"
