@@ -21,6 +21,7 @@
 // predecessor (the weights do not depend on it).
 #include "common.cuh"
 #include "mma.cuh"
+#include "tcgen05.cuh"      // TMA and mbarrier helpers, tensor-map cache
 
 namespace stride {
 namespace stream_gemm {
@@ -75,14 +76,24 @@ struct RowNorm {
 // rows [blockIdx.x * per_cta, + per_cta). MODE 2: the QKV projection with QkvEpilogue; the CTA owns per_cta rotation
 // pairs (pair p of head h is rows h * hd + p and h * hd + p + hd/2), eight per tile, rows 0-7 of the tile holding
 // the pairs' first halves and rows 8-15 their second halves, so that both halves of a pair meet in its epilogue.
-template <int NT, int MT, int WARPS, int MODE>
+// TMA: the operands come as boxes instead (64 columns of the CTA's rows, and of the tokens), one stage of a ring
+// per box pair, the rings private to the warps as before; the warp's lane 0 issues the copies, all lanes wait on the
+// stage's mbarrier and read their fragments with ldmatrix. Many warps issuing small boxes stream faster than
+// cp.async does on this GPU (see attention_decode.cu). MODE 2 then keeps a CTA's pairs inside one head (two boxes per
+// stage: the pairs' first halves and their second halves), `per_cta` pairs at `ctas_per_head` CTAs a head.
+template <int NT, int MT, int WARPS, int MODE, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int m, int n,
-                   int k, int per_cta, const QkvEpilogue qkv, const RowNorm norm) {
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ out, int m, int n,
+                   int k, int per_cta, int ctas_per_head, const QkvEpilogue qkv, const RowNorm norm, int* __restrict__ status) {
     constexpr int STAGES = ring_stages(NT, MT, WARPS);
     constexpr int THREADS = WARPS * 32;
     constexpr int PIECES = 2 * MT + NT;      // per step: rows g and g + 8 of every tile, then one piece of x per token tile
-    extern __shared__ __align__(16) uint4 ring[];        // [STAGES][kUnroll][PIECES][THREADS]
+    constexpr int W_BYTES = MT * 2048, X_BYTES = NT * 1024, STAGE_BYTES = W_BYTES + X_BYTES;      // TMA: a stage of one warp
+    extern __shared__ __align__(1024) unsigned char ring_raw[];
+    unsigned char* ring_bytes = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~uintptr_t(1023));
+    uint4* ring = reinterpret_cast<uint4*>(ring_bytes);  // cp.async: [STAGES][kUnroll][PIECES][THREADS]
+    __shared__ __align__(8) uint64_t stage_bar[TMA ? WARPS : 1][TMA ? STAGES : 1];
     __shared__ float red[WARPS][MT][NT][16][8];
     __shared__ float rstd_s[16];                          // per token: 1/rms of the norm folded into this product (1 without one)
     __shared__ float share_s[WARPS * 2][16];              // its sums of squares, one share per 16 threads
@@ -92,7 +103,12 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const int g = lane >> 2, t = lane & 3;
     const int half = qkv.hd / 2;
     const int units = MODE == 2 ? n / 2 : n;              // rows, or rotation pairs
-    const int first = blockIdx.x * per_cta, last = min(first + per_cta, units);       // this CTA's rows or pairs
+    int first = blockIdx.x * per_cta, last = min(first + per_cta, units);       // this CTA's rows or pairs
+    if (TMA && MODE == 2) {                               // pairs of one head
+        const int head = blockIdx.x / ctas_per_head, in_head = (blockIdx.x - head * ctas_per_head) * per_cta;
+        first = head * half + in_head;
+        last = head * half + min(in_head + per_cta, half);
+    }
     // the weight row behind fragment row g (lo) and g + 8 (hi) of tile mt, or -1
     const __nv_bfloat16* w_lo[MT];
     const __nv_bfloat16* w_hi[MT];
@@ -151,13 +167,48 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
+    // ---- TMA: stage i of this warp holds columns (i * WARPS + warp) * 64 .. + 63
+    const int k_stages = (k + 63) / 64;
+    const int my_stages = k_stages > warp ? (k_stages - warp + WARPS - 1) / WARPS : 0;
+    unsigned char* my_ring = ring_bytes + warp * STAGES * STAGE_BYTES;
+    bool alive = true;                                      // false once a bounded wait has run out
+    auto request_stage = [&](int i, bool weights, bool tokens) {
+        if (lane != 0 || i >= my_stages || !alive) return;
+        const int st = i % STAGES, col = (i * WARPS + warp) * 64;
+        const uint32_t bar = tc::smem_u32(&stage_bar[warp][st]), dst = tc::smem_u32(my_ring + st * STAGE_BYTES);
+        if (weights) {
+            // one arrival per stage use: the bytes of every box of the stage are announced with the first copies
+            if (MODE == 2) {
+                tc::mbar_expect_tx(bar, 2 * per_cta * 128 + NT * 8 * 128);
+                const int head = first / half, i0 = first - head * half;
+                tc::tma_load_2d(dst, &map_w, bar, col, head * qkv.hd + i0);
+                tc::tma_load_2d(dst + MT * 1024, &map_w, bar, col, head * qkv.hd + half + i0);
+            } else {
+                tc::mbar_expect_tx(bar, per_cta * 128 + NT * 8 * 128);
+                tc::tma_load_2d(dst, &map_w, bar, col, first);
+            }
+        }
+        if (tokens) tc::tma_load_2d(dst + W_BYTES, &map_x, bar, col, 0);
+    };
+    if (TMA) {
+        if (lane == 0)
+            for (int st = 0; st < STAGES; ++st) tc::mbar_init(tc::smem_u32(&stage_bar[warp][st]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
 #pragma unroll
-    for (int b = 0; b < STAGES - 1; ++b) request_weights(b);
-    pdl_wait();       // x is written by the kernel before this one
+        for (int i = 0; i < STAGES - 1; ++i) request_stage(i, true, false);
+        pdl_wait();       // x is written by the kernel before this one
 #pragma unroll
-    for (int b = 0; b < STAGES - 1; ++b) {
-        request_x(b);
-        cp_async_commit();      // group b: x of batch b (and, in group 0, the weights requested above)
+        for (int i = 0; i < STAGES - 1; ++i) request_stage(i, false, true);
+    } else {
+    #pragma unroll
+        for (int b = 0; b < STAGES - 1; ++b) request_weights(b);
+        pdl_wait();       // x is written by the kernel before this one
+#pragma unroll
+        for (int b = 0; b < STAGES - 1; ++b) {
+            request_x(b);
+            cp_async_commit();      // group b: x of batch b (and, in group 0, the weights requested above)
+        }
     }
     // The folded norm's sums of squares, while the ring fills: every thread adds up a share of the producer CTAs for
     // one token (loads first, then the sums, so that no load waits for another); the shares meet after the main loop.
@@ -189,38 +240,81 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         }
     }
 
-    for (int b = 0; b < my_batches; ++b) {
-        cp_async_wait<STAGES - 2>();       // batch b has landed; the pieces are this thread's own, so no barrier
-        uint4 wl[kUnroll][MT], wh[kUnroll][MT], xv[kUnroll][NT];
+    if (TMA) {
+        const int lm = lane >> 3, lr = lane & 7;            // ldmatrix: matrix index and row within it
+        for (int i = 0; i < my_stages; ++i) {
+            const int st = i % STAGES;
+            if (alive) alive = tc::mbar_wait(tc::smem_u32(&stage_bar[warp][st]), static_cast<uint32_t>(i / STAGES) & 1u, status, 41);
+            __syncwarp();
+            if (alive) {
+                const uint32_t ws = smem_addr(my_ring + st * STAGE_BYTES), xs = ws + W_BYTES;
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+                for (int kp = 0; kp < 2; ++kp) {            // two 16-column steps per ldmatrix of x
+                    uint32_t bx[NT][4];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                wl[u][mt] = *slot(b, u, 2 * mt);
-                wh[u][mt] = *slot(b, u, 2 * mt + 1);
+                    for (int nt = 0; nt < NT; ++nt) {       // tokens nt*8 + lr, chunks 4 kp + lm: b0, b1 of step 2 kp, then of 2 kp + 1
+                        const int row = nt * 8 + lr, chunk = 4 * kp + lm;
+                        ldmatrix_x4(bx[nt], xs + row * 128 + ((chunk ^ (row & 7)) << 4));
+                    }
+#pragma unroll
+                    for (int kk = 2 * kp; kk < 2 * kp + 2; ++kk) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            // A fragment: rows 0-7 / 8-15 of the tile, columns 16 kk .. + 15
+                            int row;
+                            uint32_t base = ws;
+                            if (MODE == 2) {                // rows 0-7: the pairs' first halves (first box), rows 8-15: their second halves
+                                row = mt * 8 + lr;
+                                base += (lm & 1) * (MT * 1024);
+                            } else {
+                                row = mt * 16 + (lm & 1) * 8 + lr;
+                            }
+                            const int chunk = 2 * kk + (lm >> 1);
+                            uint32_t a[4];
+                            ldmatrix_x4(a, base + row * 128 + ((chunk ^ (row & 7)) << 4));
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(acc[mt][nt], a, bx[nt][2 * (kk & 1)], bx[nt][2 * (kk & 1) + 1]);
+                        }
+                    }
+                }
             }
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) xv[u][nt] = *slot(b, u, 2 * MT + nt);
+            __syncwarp();                                   // every lane is done with the stage before it is refilled
+            request_stage(i + STAGES - 1, true, true);
         }
-        // the stage read in the iteration before this one is free again
-        request_weights(b + STAGES - 1);
-        request_x(b + STAGES - 1);
-        cp_async_commit();
+    } else {
+        for (int b = 0; b < my_batches; ++b) {
+            cp_async_wait<STAGES - 2>();       // batch b has landed; the pieces are this thread's own, so no barrier
+            uint4 wl[kUnroll][MT], wh[kUnroll][MT], xv[kUnroll][NT];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+            for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t f0[4] = {wl[u][mt].x, wh[u][mt].x, wl[u][mt].y, wh[u][mt].y};
-                const uint32_t f1[4] = {wl[u][mt].z, wh[u][mt].z, wl[u][mt].w, wh[u][mt].w};
+                for (int mt = 0; mt < MT; ++mt) {
+                    wl[u][mt] = *slot(b, u, 2 * mt);
+                    wh[u][mt] = *slot(b, u, 2 * mt + 1);
+                }
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    mma_bf16_16816(acc[mt][nt], f0, xv[u][nt].x, xv[u][nt].y);
-                    mma_bf16_16816(acc[mt][nt], f1, xv[u][nt].z, xv[u][nt].w);
+                for (int nt = 0; nt < NT; ++nt) xv[u][nt] = *slot(b, u, 2 * MT + nt);
+            }
+            // the stage read in the iteration before this one is free again
+            request_weights(b + STAGES - 1);
+            request_x(b + STAGES - 1);
+            cp_async_commit();
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint32_t f0[4] = {wl[u][mt].x, wh[u][mt].x, wl[u][mt].y, wh[u][mt].y};
+                    const uint32_t f1[4] = {wl[u][mt].z, wh[u][mt].z, wl[u][mt].w, wh[u][mt].w};
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma_bf16_16816(acc[mt][nt], f0, xv[u][nt].x, xv[u][nt].y);
+                        mma_bf16_16816(acc[mt][nt], f1, xv[u][nt].z, xv[u][nt].w);
+                    }
                 }
             }
         }
+        cp_async_wait<0>();
     }
-    cp_async_wait<0>();
 
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -327,18 +421,22 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     }
 }
 
-template <int NT, int MT, int WARPS, int MODE>
-int launch_warps(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, int per_cta, int ctas,
-                 const QkvEpilogue& qkv, const RowNorm& norm, cudaStream_t stream) {
-    constexpr int smem = ring_stages(NT, MT, WARPS) * kUnroll * (2 * MT + NT) * WARPS * 32 * 16;
-    auto kernel = gemm_stream_kernel<NT, MT, WARPS, MODE>;
+template <int NT, int MT, int WARPS, int MODE, bool TMA>
+int launch_warps(const CUtensorMap* map_w, const CUtensorMap* map_x, const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m,
+                 int n, int k, int per_cta, int ctas_per_head, int ctas, const QkvEpilogue& qkv, const RowNorm& norm, int* status,
+                 cudaStream_t stream) {
+    constexpr int smem = (TMA ? ring_stages(NT, MT, WARPS) * WARPS * (MT * 2048 + NT * 1024)
+                              : ring_stages(NT, MT, WARPS) * kUnroll * (2 * MT + NT) * WARPS * 32 * 16) + 1024;
+    auto kernel = gemm_stream_kernel<NT, MT, WARPS, MODE, TMA>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    stride::launch(kernel, dim3(static_cast<unsigned>(ctas)), dim3(WARPS * 32), smem, stream, x, w, out, m, n, k, per_cta, qkv, norm);
+    static const CUtensorMap no_map = {};
+    stride::launch(kernel, dim3(static_cast<unsigned>(ctas)), dim3(WARPS * 32), smem, stream, TMA ? *map_w : no_map, TMA ? *map_x : no_map,
+                   x, w, out, m, n, k, per_cta, ctas_per_head, qkv, norm, status);
     return STRIDE_LAUNCH_STATUS();
 }
 
@@ -351,42 +449,90 @@ inline int sm_count() {
     return count;
 }
 
+// STRIDE_STREAM_TMA=0 keeps the cp.async copies (for comparisons).
+inline bool stream_tma_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("STRIDE_STREAM_TMA");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 // Rows (MODE 2: rotation pairs) per CTA and the number of CTAs: one CTA per SM with equal shares when a CTA's
 // kMaxTiles tiles can hold such a share, else full CTAs of kMaxTiles tiles; a short K (small models) gets one tile
-// per CTA and fewer warps.
+// per CTA and fewer warps. With TMA copies a MODE 2 CTA stays inside one head: `ctas_per_head` CTAs of `per_cta`
+// pairs each (the last one of a head may hold fewer).
 struct Shape {
-    int per_cta, ctas, tiles, warps;
+    int per_cta, ctas, tiles, warps, ctas_per_head;
+    bool tma;
 };
-inline Shape shape_for(int n, int k, int mode) {
+inline Shape shape_for(int n, int k, int mode, int hd, bool tma_possible) {
     const int batches = ((k + kStepCols - 1) / kStepCols + kUnroll - 1) / kUnroll;
     const int units = mode == 2 ? n / 2 : n, per_tile = mode == 2 ? 8 : 16;
-    Shape s;
+    Shape s{};
+    s.ctas_per_head = 1;
     if (batches < 8 * 4) {
         s.per_cta = per_tile;
         s.tiles = 1;
         s.warps = batches >= 4 * 4 ? 4 : 2;
-    } else {
-        s.per_cta = (units + sm_count() - 1) / sm_count();
-        if (s.per_cta > kMaxTiles * per_tile) s.per_cta = kMaxTiles * per_tile;
-        s.tiles = (s.per_cta + per_tile - 1) / per_tile;
-        s.warps = 8;
+        s.ctas = (units + s.per_cta - 1) / s.per_cta;
+        return s;
     }
+    s.warps = 8;
+    s.per_cta = (units + sm_count() - 1) / sm_count();
+    if (s.per_cta > kMaxTiles * per_tile) s.per_cta = kMaxTiles * per_tile;
+    s.tma = tma_possible && stream_tma_enabled();
+    if (s.tma && mode == 2) {
+        const int half = hd / 2;
+        int per_head = (half + s.per_cta / 2) / s.per_cta;          // rounded: CTAs a head is cut into
+        if (per_head < 1) per_head = 1;
+        const int pairs = (half + per_head - 1) / per_head;
+        if (pairs > kMaxTiles * per_tile) {
+            s.tma = false;
+        } else {
+            s.ctas_per_head = per_head;
+            s.per_cta = pairs;
+            s.tiles = (pairs + per_tile - 1) / per_tile;
+            s.ctas = (units / half) * per_head;
+            return s;
+        }
+    }
+    s.tiles = (s.per_cta + per_tile - 1) / per_tile;
     s.ctas = (units + s.per_cta - 1) / s.per_cta;
     return s;
 }
 
 template <int NT, int MODE>
-int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream,
+int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, void* out, int m, int n, int k, cudaStream_t stream, int* status,
                   const QkvEpilogue& qkv = QkvEpilogue{}, const RowNorm& norm = RowNorm{}) {
-    const Shape s = shape_for(n, k, MODE);
-    if (s.warps == 4) return launch_warps<NT, 1, 4, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
-    if (s.warps == 2) return launch_warps<NT, 1, 2, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
-    switch (s.tiles) {
-        case 1: return launch_warps<NT, 1, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
-        case 2: return launch_warps<NT, 2, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
-        case 3: return launch_warps<NT, 3, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
-        default: return launch_warps<NT, 4, 8, MODE>(x, w, out, m, n, k, s.per_cta, s.ctas, qkv, norm, stream);
+    Shape s = shape_for(n, k, MODE, qkv.hd, status != nullptr);
+    const CUtensorMap* map_w = nullptr;
+    const CUtensorMap* map_x = nullptr;
+    if (s.tma) {
+        map_w = tc::cached_map(w, n, k, k, s.per_cta);
+        map_x = tc::cached_map(x, m, k, k, NT * 8);
+        if (map_w == nullptr || map_x == nullptr) s = shape_for(n, k, MODE, qkv.hd, false);
     }
+#define STRIDE_STREAM_LAUNCH(MT_, WARPS_, TMA_)                                                                                 \
+    launch_warps<NT, MT_, WARPS_, MODE, TMA_>(map_w, map_x, x, w, out, m, n, k, s.per_cta, s.ctas_per_head, s.ctas, qkv, norm, status, \
+                                              stream)
+    if (s.warps == 4) return STRIDE_STREAM_LAUNCH(1, 4, false);
+    if (s.warps == 2) return STRIDE_STREAM_LAUNCH(1, 2, false);
+    if (s.tma) {
+        switch (s.tiles) {
+            case 1: return STRIDE_STREAM_LAUNCH(1, 8, true);
+            case 2: return STRIDE_STREAM_LAUNCH(2, 8, true);
+            case 3: return STRIDE_STREAM_LAUNCH(3, 8, true);
+            default: return STRIDE_STREAM_LAUNCH(4, 8, true);
+        }
+    }
+    switch (s.tiles) {
+        case 1: return STRIDE_STREAM_LAUNCH(1, 8, false);
+        case 2: return STRIDE_STREAM_LAUNCH(2, 8, false);
+        case 3: return STRIDE_STREAM_LAUNCH(3, 8, false);
+        default: return STRIDE_STREAM_LAUNCH(4, 8, false);
+    }
+#undef STRIDE_STREAM_LAUNCH
 }
 
 }  // namespace stream_gemm
@@ -398,17 +544,17 @@ using namespace stride;
 // out: [tokens, n_out], bf16 (out_is_f32 == 0) or float32. Returns -2 for what it does not take
 // (more than 16 tokens, unaligned operands); the caller then uses another product.
 extern "C" int stride_gemm_stream_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int k, int out_is_f32,
-                                       cudaStream_t stream) {
+                                       int* status, cudaStream_t stream) {
     if (tokens < 0 || n_out <= 0 || k <= 0) return STRIDE_BAD_ARGUMENT;
     if (tokens > 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
     auto xp = static_cast<const __nv_bfloat16*>(x);
     auto wp = static_cast<const __nv_bfloat16*>(w);
     if (tokens <= 8)
-        return out_is_f32 ? stream_gemm::launch_stream<1, 1>(xp, wp, out, tokens, n_out, k, stream)
-                          : stream_gemm::launch_stream<1, 0>(xp, wp, out, tokens, n_out, k, stream);
-    return out_is_f32 ? stream_gemm::launch_stream<2, 1>(xp, wp, out, tokens, n_out, k, stream)
-                      : stream_gemm::launch_stream<2, 0>(xp, wp, out, tokens, n_out, k, stream);
+        return out_is_f32 ? stream_gemm::launch_stream<1, 1>(xp, wp, out, tokens, n_out, k, stream, status)
+                          : stream_gemm::launch_stream<1, 0>(xp, wp, out, tokens, n_out, k, stream, status);
+    return out_is_f32 ? stream_gemm::launch_stream<2, 1>(xp, wp, out, tokens, n_out, k, stream, status)
+                      : stream_gemm::launch_stream<2, 0>(xp, wp, out, tokens, n_out, k, stream, status);
 }
 
 // The projection of queries, keys and values for at most 16 tokens with rotation and cache write in its
@@ -420,7 +566,7 @@ extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* q
                                            const int32_t* slot_mapping, const float* cos_table, const float* sin_table,
                                            void* k_pages, void* v_pages, int tokens, int nq, int nkv, int hd, int page_size,
                                            int k, int rotate, const float* norm_partials, int norm_count, float norm_eps,
-                                           cudaStream_t stream) {
+                                           int* status, cudaStream_t stream) {
     if (tokens < 0 || nq <= 0 || nkv <= 0 || hd <= 0 || page_size <= 0 || k <= 0 || positions == nullptr) return STRIDE_BAD_ARGUMENT;
     if (tokens > 16 || hd % 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
     if (tokens == 0) return 0;
@@ -437,8 +583,8 @@ extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* q
         norm.inv_width = 1.f / static_cast<float>(k);
         norm.eps = norm_eps;
     }
-    if (tokens <= 8) return stream_gemm::launch_stream<1, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e, norm);
-    return stream_gemm::launch_stream<2, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, e, norm);
+    if (tokens <= 8) return stream_gemm::launch_stream<1, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, status, e, norm);
+    return stream_gemm::launch_stream<2, 2>(xp, wp, qkv_out, tokens, n_out, k, stream, status, e, norm);
 }
 
 // The product before an RMS norm, for at most 16 tokens: residual [tokens, n_out] float32 += bf16(x @ w^T),
@@ -447,11 +593,11 @@ extern "C" int stride_gemm_stream_qkv_rope(const void* x, const void* w, void* q
 // what it does not take, -1 if `partials_capacity` (floats) is too small.
 extern "C" int stride_gemm_stream_add_norm(const void* x, const void* w, void* xtilde, float* residual, const float* norm_weight,
                                            float* partials, long long partials_capacity, int tokens, int n_out, int k,
-                                           int* ctas_out, cudaStream_t stream) {
+                                           int* ctas_out, int* status, cudaStream_t stream) {
     if (tokens < 0 || n_out <= 0 || k <= 0 || residual == nullptr || norm_weight == nullptr || partials == nullptr || ctas_out == nullptr)
         return STRIDE_BAD_ARGUMENT;
     if (tokens > 16 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
-    const stream_gemm::Shape shape = stream_gemm::shape_for(n_out, k, 3);
+    const stream_gemm::Shape shape = stream_gemm::shape_for(n_out, k, 3, 0, status != nullptr);
     if (partials_capacity < static_cast<long long>(shape.ctas) * 16) return STRIDE_BAD_ARGUMENT;
     *ctas_out = shape.ctas;
     if (tokens == 0) return 0;
@@ -461,6 +607,6 @@ extern "C" int stride_gemm_stream_add_norm(const void* x, const void* w, void* x
     norm.out_partials = partials;
     auto xp = static_cast<const __nv_bfloat16*>(x);
     auto wp = static_cast<const __nv_bfloat16*>(w);
-    if (tokens <= 8) return stream_gemm::launch_stream<1, 3>(xp, wp, xtilde, tokens, n_out, k, stream, stream_gemm::QkvEpilogue{}, norm);
-    return stream_gemm::launch_stream<2, 3>(xp, wp, xtilde, tokens, n_out, k, stream, stream_gemm::QkvEpilogue{}, norm);
+    if (tokens <= 8) return stream_gemm::launch_stream<1, 3>(xp, wp, xtilde, tokens, n_out, k, stream, status, stream_gemm::QkvEpilogue{}, norm);
+    return stream_gemm::launch_stream<2, 3>(xp, wp, xtilde, tokens, n_out, k, stream, status, stream_gemm::QkvEpilogue{}, norm);
 }

@@ -42,12 +42,12 @@ _SIGNATURES = {
                                                              c_int, c_int, c_void_p]),
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
-    "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_qkv_rope": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                         c_void_p, c_int, c_float, c_void_p]),
+                                                         c_void_p, c_int, c_float, c_void_p, c_void_p]),
     "stride_gemm_stream_add_norm": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
-                                                         c_int, c_int, c_int, c_void_p, c_void_p]),
+                                                         c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "stride_scale_rows": ("elementwise", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
@@ -312,7 +312,7 @@ def linear_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
     code = _fn("stride_gemm_stream_add_norm")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
                                               _dev(xt, "xt", torch.bfloat16), _dev(residual, "residual", torch.float32),
                                               _dev(norm_weight, "norm_weight", torch.float32), _dev(partials, "partials", torch.float32),
-                                              partials.numel(), m, n, k, ctypes.byref(count), _stream())
+                                              partials.numel(), m, n, k, ctypes.byref(count), _status_ptr(x.device), _stream())
     if code == -2:
         return 0
     _check(code, "gemm_stream_add_norm")
@@ -339,13 +339,17 @@ def linear_gated_tc(x, weight, out, folded=None) -> bool:
     return True
 
 
+def _status_ptr(device) -> int:
+    return _tc_buffers(device, 0)["status"].data_ptr()
+
+
 def linear_stream(x, weight, out) -> bool:
     """``out = x @ weight.T`` on the weight-streaming kernel (at most 16 rows of ``x``).
     Returns False when the kernel does not take the shape."""
     m, k = x.shape
     n = weight.shape[0]
     code = _fn("stride_gemm_stream_bf16")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
-                                          m, n, k, int(out.dtype == torch.float32), _stream())
+                                          m, n, k, int(out.dtype == torch.float32), _status_ptr(x.device), _stream())
     if code == -2:
         return False
     _check(code, "gemm_stream_bf16")
@@ -367,7 +371,8 @@ def linear_qkv_rope(x, weight, qkv, bias, positions, slot_mapping, cos, sin, k_p
         _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(qkv, "qkv", torch.bfloat16),
         _opt(bias, "bias", torch.float32), _dev(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
         _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages", torch.bfloat16),
-        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), partials, count, eps, _stream())
+        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), partials, count, eps,
+        _status_ptr(x.device), _stream())
     if code == -2:
         return False
     _check(code, "gemm_stream_qkv_rope")
