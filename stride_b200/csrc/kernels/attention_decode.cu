@@ -31,7 +31,7 @@ namespace stride {
 
 constexpr int kTileKeys = 16;     // keys one warp works on at a time
 constexpr int kGroupKeys = 64;    // keys the four warps of a CTA cover per pipeline stage
-constexpr int kStages = 2;
+constexpr int kStages = 2;        // three stages (two CTAs per SM) measured 1 % slower at batch 8, 1 % faster at batch 1
 constexpr int kTicketInts = 65536;   // ticket counters at the start of the scratch, one per (token, key head)
 
 // TMA: the 16-key tiles (16 keys of one head never straddle a page when the page size is a multiple of 16) come as
@@ -147,13 +147,13 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     };
     const bool holds_newest = pos < lo + split_keys;      // the key written by the kernel before this one is in this split
     if (!holds_newest) {
-        issue(0);
-        issue(1);
+#pragma unroll
+        for (int st = 0; st < kStages; ++st) issue(st);
     }
     pdl_wait();
     if (holds_newest) {
-        issue(0);
-        issue(1);
+#pragma unroll
+        for (int st = 0; st < kStages; ++st) issue(st);
     }
 
     // The query group as the A operand: row r is query head kvh * group + r.

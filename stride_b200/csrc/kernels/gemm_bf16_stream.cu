@@ -8,7 +8,9 @@
 // token g of x, as 16-byte pieces, and feeds them to two products (columns 0-3, then 4-7):
 // every thread consumes exactly the pieces it fetched itself. The pieces travel by cp.async
 // into a ring in shared memory that is private to the thread (no barrier, only
-// cp.async.wait_group), several batches ahead. Shared memory rather than registers as the
+// cp.async.wait_group), several batches ahead. (That is the path for short K and the fallback;
+// for the matrices of a real model the operands come as TMA boxes into rings private to the
+// warps and the fragments are read with ldmatrix: see the TMA note at the kernel.) Shared memory rather than registers as the
 // landing zone on purpose: plain loads in flight live in the L1 part of the SM's memory, and
 // when this kernel shares an SM with kernels that have configured it for shared memory (which
 // programmatic dependent launch makes the normal case), almost no L1 is left and a load-based
