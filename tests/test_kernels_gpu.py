@@ -410,6 +410,53 @@ def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
     assert not ops.fast_attention_supported(torch.float32, 4, 2, 128)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(8, 2, 128, 16, None), (4, 1, 64, 32, None), (8, 2, 128, 16, 3000)])
+def test_decode_attention_long_contexts(ops, nq, nkv, hd, page, window):
+    """Tens of splits of up to 1,024 keys, each walked in many tiles; one far key per request carries nearly all
+    of the weight, so a split that is dropped, merged twice or read from the wrong page shows. The plain result
+    is the one-row formula softmax(q K^T * scale) V in float64 (python/stride_worker/layers.py:128-149)."""
+    g = torch.Generator().manual_seed(31)
+    dtype = torch.bfloat16
+    contexts, far = [20000, 9001, 33000, 1], [1234, 8000, 31999, 0]
+    pages_of = [-(-n // page) for n in contexts]
+    perm = torch.randperm(sum(pages_of) + 3, generator=g).tolist()
+    k_pages = torch.zeros(sum(pages_of) + 3, nkv, page, hd)
+    v_pages = torch.zeros_like(k_pages)
+    table = torch.full((len(contexts), max(pages_of) + 1), -1, dtype=torch.int32)
+    qs, wants = [], []
+    for s, (n, kj) in enumerate(zip(contexts, far)):
+        q = torch.randn(nq, hd, generator=g)
+        k = torch.randn(n, nkv, hd, generator=g)
+        v = torch.randn(n, nkv, hd, generator=g)
+        if window is None or n - 1 - kj < window:
+            k[kj] = q.view(nkv, nq // nkv, hd)[:, 0] * 2.0
+        q, k, v = q.to(dtype).double(), k.to(dtype).double(), v.to(dtype).double()
+        for p in range(pages_of[s]):
+            table[s, p] = perm.pop()
+            lo, hi = p * page, min(n, (p + 1) * page)
+            k_pages[table[s, p], :, :hi - lo] = k[lo:hi].transpose(0, 1).float()
+            v_pages[table[s, p], :, :hi - lo] = v[lo:hi].transpose(0, 1).float()
+        first = 0 if window is None else max(0, n - window)
+        rows = []
+        for h in range(nq):
+            kh = h // (nq // nkv)
+            w = torch.softmax(k[first:, kh] @ q[h] * hd ** -0.5, 0)
+            rows.append(w @ v[first:, kh])
+        qs.append(q.reshape(-1))
+        wants.append(torch.cat(rows))
+    q = torch.stack(qs).to(dtype)
+    want = torch.stack(wants).float()
+    seq_of = torch.arange(len(contexts), dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in contexts], dtype=torch.int32)
+    for bound in (33000, 131072):
+        scratch = torch.full((ops.decode_scratch_floats(q.shape[0], nq, nkv, hd, bound),), float("nan"), device="cuda")
+        scratch[:65536] = 0
+        out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+        ops.paged_attention_decode(dev(q), nq * hd, out, dev(k_pages.to(dtype)), dev(v_pages.to(dtype)), dev(table), dev(seq_of),
+                                   dev(pos), scratch, nq, nkv, hd, page, hd ** -0.5, window or 0, bound)
+        close(out, want, dtype)
+
+
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [
     (8, 2, 128, 16, None), (3, 1, 64, 8, None), (4, 4, 128, 32, None), (8, 2, 128, 16, 70), (6, 2, 64, 16, 5), (4, 1, 128, 16, 64),
 ])
