@@ -116,6 +116,19 @@ class LlamaConfig:
         cfg.validate()
         return cfg
 
+    @staticmethod
+    def complete_from_checkpoint(d: dict, tensor_names: set) -> dict:
+        """Two options that the reference settles by what the checkpoint holds, never by config.json
+        (python/stride_worker/model.py:127-128,159-169): the head is tied when ``lm_head.weight`` is absent,
+        and the q/k/v projections have biases when the bias tensors are there. A config.json that gives the
+        key is taken at its word (and checked against the checkpoint at load); one that leaves it out gets it
+        from the checkpoint here."""
+        if "tie_word_embeddings" not in d:
+            d["tie_word_embeddings"] = "lm_head.weight" not in tensor_names
+        if "attention_bias" not in d:
+            d["attention_bias"] = any(n.endswith(".self_attn.q_proj.bias") for n in tensor_names)
+        return d
+
     def validate(self) -> None:
         if self.num_attention_heads % self.num_key_value_heads:
             raise ConfigError(f"{self.num_attention_heads} query heads do not divide evenly into "
@@ -249,4 +262,4 @@ def _read_rope_scaling(raw) -> Optional[RopeScaling]:
     return s
 
 
-register_architecture("LlamaForCausalLM", LlamaConfig)
+register_architecture("LlamaForCausalLM", LlamaConfig, model_type="llama")

@@ -24,11 +24,10 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
-from ..config import EngineConfig, config_from_dict, load_config
+from ..config import EngineConfig, config_from_dict
 from ..csrc import ops
 from ..csrc.build import load_runtime
-from ..weights import SafetensorsSource
-from .loading import attach_cache, build_model, plan_cache, random_model
+from .loading import attach_cache, load_model, plan_cache, random_model
 from .runner import ModelRunner
 
 
@@ -70,8 +69,7 @@ class Engine:
         token_cap = self.cfg.max_batch_tokens
         row_cap = min(self.cfg.max_batch_seqs, token_cap)
         if model is not None:
-            self.model_config = load_config(model)
-            self.model = build_model(self.model_config, SafetensorsSource(model), self.cfg.dtype, device, token_cap, row_cap)
+            self.model_config, self.model = load_model(model, self.cfg.dtype, device, token_cap, row_cap)
         elif config is not None:
             self.model_config = config_from_dict(config) if isinstance(config, dict) else config
             if random_weights is None:

@@ -28,8 +28,9 @@ def build_model(config, source, dtype: str, device="cuda", token_capacity: int =
 
 
 def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda", token_capacity: int = 2048, row_capacity: int = 256):
-    config = load_config(model_dir)
-    return config, build_model(config, SafetensorsSource(model_dir), dtype, device, token_capacity, row_capacity)
+    source = SafetensorsSource(model_dir)
+    config = load_config(model_dir, tensor_names=source.names())
+    return config, build_model(config, source, dtype, device, token_capacity, row_capacity)
 
 
 def random_model(config, seed: int, dtype: str = "bfloat16", device="cuda", token_capacity: int = 2048,

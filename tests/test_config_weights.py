@@ -46,13 +46,29 @@ def test_defaults_follow_the_reference_and_required_keys_are_required():
     ({"num_key_value_heads": 3}, "do not divide"), ({"hidden_act": "gelu"}, "hidden_act"), ({"mlp_bias": True}, "mlp_bias"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"), ({"vocab_size": 0}, "vocab_size"),
     ({"hidden_size": "64"}, "hidden_size"), ({"head_dim": 15}, "even"), ({"architectures": ["GPT2LMHeadModel"]}, "LlamaForCausalLM"),
-    ({"architectures": []}, "names no architecture"), ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
+    ({"architectures": [], "model_type": "other"}, "names no architecture"), ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
 ])
 def test_bad_configs_are_refused(change, match):
     d = dict(TINY["A"])
     d.update(change)
     with pytest.raises(ConfigError, match=match):
         config_from_dict(d)
+
+
+def test_what_config_json_leaves_out_is_settled_as_the_reference_does():
+    """No ``architectures``: placed by ``model_type``. No ``tie_word_embeddings`` or ``attention_bias``: the
+    checkpoint's contents decide (python/stride_worker/model.py:127-128,159-169); a key that is given stands."""
+    d = {k: v for k, v in TINY["A"].items() if k not in ("architectures", "tie_word_embeddings")}
+    assert type(config_from_dict(d)) is LlamaConfig
+    names = {"model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.q_proj.bias"}
+    c = config_from_dict(d, tensor_names=names)
+    assert c.tie_word_embeddings and c.attention_bias
+    c = config_from_dict(d, tensor_names=(names - {"model.layers.0.self_attn.q_proj.bias"}) | {"lm_head.weight"})
+    assert not c.tie_word_embeddings and not c.attention_bias
+    given = dict(d, tie_word_embeddings=False, attention_bias=False)
+    c = config_from_dict(given, tensor_names=names)
+    assert not c.tie_word_embeddings and not c.attention_bias
+    assert not config_from_dict(d).tie_word_embeddings, "without a checkpoint the default of the reference stands"
 
 
 def test_registry_and_round_trip(tmp_path):
