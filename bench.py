@@ -35,7 +35,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_burst": 1590.0, "source": "fallback"}
 
 
 def peaks() -> dict:
@@ -44,8 +44,10 @@ def peaks() -> dict:
         try:
             with open(path) as f:
                 d = json.load(f)
+            # The prefill is a long step of several hundred kernels under the power cap, so its fraction is taken
+            # of the library product's sustained rate; the burst rate is reported beside it.
             return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]),
-                    "source": "measured"}
+                    "bf16_tflops_burst": float(d["bf16_tflops"]), "source": "measured"}
         except (ValueError, KeyError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -201,7 +203,8 @@ def run_ours(args) -> dict:
             times.append(start.elapsed_time(end))
     prefill_ms = statistics.median(times)
     prefill = {"value": round(prompt_len / prefill_ms * 1e3, 1), "tokens": prompt_len, "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "frac_of_burst_peak": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
 
     # ---- decode points, device-timed graph replays on synthetic caches
     points, key_base = {}, 1000

@@ -130,6 +130,29 @@ def cmd_replay(args) -> int:
     return 0
 
 
+def cmd_diagnose_prefill(args) -> int:
+    """Portions against the whole prompt, logits of the last token (the reference's ``stride-diagnose prefill``,
+    python/stride_worker/diagnose/cli.py:44-73)."""
+    from .diagnose import report
+    from .diagnose.prefill import PrefillProbe, seeded_prompt
+    from .engine.trace import TraceSession
+
+    session = TraceSession(args.model, dtype=args.dtype, max_tokens=-(-args.tokens // 64) * 64, block_size=args.block_size,
+                           max_requests=2)
+    tokens = seeded_prompt(session.model.vocab, args.tokens, args.seed)
+    sizes = [int(s) for s in args.chunk.split(",") if s.strip()]
+    print(f"prompt: {len(tokens)} tokens, chunk sizes {sizes}\n")
+    all_ok = True
+    for size, agreement in PrefillProbe(session).sweep(tokens, sizes).items():
+        ok, _ = agreement.verdict(args.dtype)
+        all_ok &= ok
+        print(report(f"chunk={size}", agreement, args.dtype))
+        print()
+    print("Portions match the whole prompt." if all_ok else
+          "Portions do not match the whole prompt: look at the mask and the position arithmetic at a portion's first token.")
+    return 0 if all_ok else 1
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="stride-b200", description="LLM inference engine for one B200 (Llama 3 dense decoder)")
     sub = parser.add_subparsers(dest="command", required=True)
@@ -159,6 +182,17 @@ def main(argv=None) -> int:
     t.add_argument("--block-size", type=int, default=16)
     t.add_argument("--max-requests", type=int, default=8)
     t.set_defaults(run=cmd_replay)
+
+    d = sub.add_parser("diagnose", help="probes of the engine's numerics")
+    dsub = d.add_subparsers(dest="probe", required=True)
+    dp = dsub.add_parser("prefill", help="a prompt in portions against the prompt whole")
+    dp.add_argument("--model", required=True)
+    dp.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    dp.add_argument("--tokens", type=int, default=5000)
+    dp.add_argument("--chunk", default="512,1024,2048", help="comma-separated portion sizes")
+    dp.add_argument("--seed", type=int, default=0)
+    dp.add_argument("--block-size", type=int, default=16)
+    dp.set_defaults(run=cmd_diagnose_prefill)
 
     args = parser.parse_args(argv)
     if args.command == "random-model" and not (args.preset or args.config):

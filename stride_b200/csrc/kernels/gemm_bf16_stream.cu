@@ -37,10 +37,14 @@ __device__ __forceinline__ void cp_async_16_or_zero(void* smem, const void* gmem
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem)), "l"(gmem), "r"(bytes));
 }
 
-// Ring depth in batches: what fits into about 200 KB for 256 threads, four at most (deeper measured the same).
+// Ring depth in batches: what fits into about STRIDE_STREAM_RING_KB for 256 threads, four at most (deeper measured
+// the same), two at least.
+#ifndef STRIDE_STREAM_RING_KB
+#define STRIDE_STREAM_RING_KB 200
+#endif
 __host__ __device__ constexpr int ring_stages(int nt, int mt, int warps) {
     const int per_stage = kUnroll * (2 * mt + nt) * warps * 32 * 16;
-    const int fit = (200 * 1024) / per_stage;
+    const int fit = (STRIDE_STREAM_RING_KB * 1024) / per_stage;
     return fit > 4 ? 4 : (fit < 2 ? 2 : fit);
 }
 
