@@ -130,6 +130,27 @@ def cmd_replay(args) -> int:
     return 0
 
 
+def cmd_plan(args) -> int:
+    """Weights, activation reserve and cache pages for a model on one device, without loading anything
+    (the reference's planner, crates/stride-model/examples/plan.rs, and its server's ``--dry-run``)."""
+    from .config import PlanError, config_from_dict, load_config, plan_memory, preset
+
+    if args.model:
+        config = load_config(args.model)
+    else:
+        config = config_from_dict(preset(args.preset) if args.preset else json.load(open(args.config)))
+    try:
+        plan = plan_memory(config, args.dtype, int(args.memory_gib * (1 << 30)), args.block_size, args.activation_reserve,
+                           name=args.preset or args.model or args.config)
+    except PlanError as e:
+        print(f"does not fit: {e}", file=sys.stderr)
+        return 1
+    print(plan.describe())
+    for context in args.context:
+        print(f"  requests of {context:<7} {plan.concurrent_sequences(context):9d}      at once")
+    return 0
+
+
 def cmd_diagnose_prefill(args) -> int:
     """Portions against the whole prompt, logits of the last token (the reference's ``stride-diagnose prefill``,
     python/stride_worker/diagnose/cli.py:44-73)."""
@@ -183,6 +204,17 @@ def main(argv=None) -> int:
     t.add_argument("--max-requests", type=int, default=8)
     t.set_defaults(run=cmd_replay)
 
+    pl = sub.add_parser("plan", help="what fits: weights, activation reserve and cache pages on one device (no GPU needed)")
+    pl.add_argument("--model", help="folder with config.json")
+    pl.add_argument("--preset")
+    pl.add_argument("--config")
+    pl.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    pl.add_argument("--memory-gib", type=float, default=183359 / 1024, help="device memory (default: a B200)")
+    pl.add_argument("--block-size", type=int, default=16)
+    pl.add_argument("--activation-reserve", type=float, default=0.15)
+    pl.add_argument("--context", type=int, action="append", default=[], help="also print how many requests of this length fit; repeatable")
+    pl.set_defaults(run=cmd_plan)
+
     d = sub.add_parser("diagnose", help="probes of the engine's numerics")
     dsub = d.add_subparsers(dest="probe", required=True)
     dp = dsub.add_parser("prefill", help="a prompt in portions against the prompt whole")
@@ -197,6 +229,8 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     if args.command == "random-model" and not (args.preset or args.config):
         parser.error("random-model needs --preset or --config")
+    if args.command == "plan" and not (args.model or args.preset or args.config):
+        parser.error("plan needs --model, --preset or --config")
     return args.run(args)
 
 

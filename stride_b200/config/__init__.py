@@ -1,5 +1,6 @@
 from .engine import DTYPES, EngineConfig
 from .llama import LlamaConfig
+from .memory import B200_MEMORY_BYTES, MemoryPlan, PlanError, plan_memory
 from .presets import PRESETS, preset
 from .registry import (ConfigError, config_class_for, config_from_dict, load_config, register_architecture,
                        registered_architectures)
@@ -7,7 +8,7 @@ from .specs import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, 
                     default_schedule)
 
 __all__ = [
-    "DTYPES", "EngineConfig", "LlamaConfig", "PRESETS", "preset", "ConfigError", "config_class_for", "config_from_dict",
+    "DTYPES", "EngineConfig", "LlamaConfig", "MemoryPlan", "PlanError", "plan_memory", "B200_MEMORY_BYTES", "PRESETS", "preset", "ConfigError", "config_class_for", "config_from_dict",
     "load_config", "register_architecture", "registered_architectures", "FeedForwardSpec", "LayerSpec", "MixerSpec",
     "ModelSpec", "NormSpec", "PositionSpec", "RopeScaling", "ScheduleEntry", "default_schedule",
 ]

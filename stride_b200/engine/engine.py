@@ -17,6 +17,7 @@ generator supplies the uniform number.
 
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 from typing import Optional, Sequence
@@ -29,6 +30,9 @@ from ..csrc import ops
 from ..csrc.build import load_runtime
 from .loading import attach_cache, load_model, plan_cache, random_model
 from .runner import ModelRunner
+
+
+_NVTX = os.environ.get("STRIDE_B200_NVTX", "0") == "1"      # named ranges around every step, for a timeline profiler
 
 
 @dataclass
@@ -102,6 +106,7 @@ class Engine:
         self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)     # the kernels' timed-out-wait word, read back with the tokens
         self._row_cap = row_cap
         self.forward_passes = 0
+        self.last_step: dict = {}
         self.busy_us = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -161,11 +166,18 @@ class Engine:
             return []
         started = time.perf_counter()
         step_batch = self.scheduler.build_batch(batch)
+        if _NVTX:
+            torch.cuda.nvtx.range_push(f"stride.step tokens={step_batch.num_tokens} seqs={step_batch.num_seqs}")
         logits = self.runner.step(step_batch)
         seqs = step_batch.row_requests()
         tokens = self._sample(logits, seqs)
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
         self.scheduler.after_step(batch)
         duration = int((time.perf_counter() - started) * 1e6)
+        # the record of the step (python/stride_worker/model.py:238-240,343-345 measures the same span on the worker)
+        self.last_step = {"tokens": step_batch.num_tokens, "seqs": step_batch.num_seqs, "rows": len(seqs),
+                          "decode_only": step_batch.decode_only, "us": duration}
         self.forward_passes += 1
         self.busy_us += duration
         self.now += max(duration, 1)

@@ -205,3 +205,43 @@ def test_random_weights_are_seeded_and_written_as_a_model_folder(tmp_path):
     order1 = [src.read(n) for n in sorted(src.names())]
     order2 = [src.read(n) for n in sorted(src.names(), reverse=True)][::-1]
     assert all(torch.equal(x, y) for x, y in zip(order1, order2)), "a tensor's values depend on the order of reads"
+
+
+def test_the_memory_plan_subtracts_weights_and_reserve_and_refuses_what_cannot_run():
+    """crates/stride-model/src/memory.rs:67-121 on one device: the cache is what weights and the reserve leave."""
+    from stride_b200.config import B200_MEMORY_BYTES, PlanError, plan_memory
+    c8 = config_from_dict(preset("llama3.1-8b"))
+    plan = plan_memory(c8, "bfloat16", block_size=16, activation_fraction=0.15)
+    matrices = c8.total_params(with_norms=False)
+    assert plan.weight_bytes == matrices * 2 + (c8.total_params() - matrices) * 4
+    after = B200_MEMORY_BYTES - plan.weight_bytes
+    assert plan.activation_reserve_bytes == int(after * 0.15) and plan.kv_bytes == after - plan.activation_reserve_bytes
+    assert plan.kv_bytes_per_token == 131072 and plan.num_blocks == plan.kv_bytes // (131072 * 16)
+    assert plan.max_context() == plan.num_blocks * 16
+    assert plan.concurrent_sequences(8192) == plan.num_blocks // 512 and plan.concurrent_sequences(0) == 0
+    assert plan.concurrent_sequences(8193) == plan.num_blocks // 513
+    assert "pages of 16" in plan.describe()
+    # the 70B shape in bfloat16 leaves tens of GiB of pages on one B200; in float32 its weights alone do not fit
+    c70 = config_from_dict(preset("llama3.1-70b"))
+    p70 = plan_memory(c70, "bfloat16")
+    assert 130 < p70.weight_bytes / 2**30 < 133 and p70.kv_bytes_per_token == 327680 and p70.total_kv_tokens > 90_000
+    with pytest.raises(PlanError, match="weights need"):
+        plan_memory(c70, "float32")
+    with pytest.raises(PlanError, match="one page"):
+        plan_memory(c8, "bfloat16", memory_bytes=plan.weight_bytes + 1_000_000)
+    with pytest.raises(PlanError):
+        plan_memory(c8, "float16")
+    with pytest.raises(PlanError):
+        plan_memory(c8, activation_fraction=1.0)
+    # a larger reserve or a float32 cache leaves fewer pages
+    assert plan_memory(c8, activation_fraction=0.5).num_blocks < plan.num_blocks
+    assert plan_memory(c8, "float32").kv_bytes_per_token == 262144
+
+
+def test_the_plan_command_line(capsys):
+    from stride_b200.cli import main
+    assert main(["plan", "--preset", "llama3.2-3b", "--context", "4096"]) == 0
+    out = capsys.readouterr().out
+    assert "llama3.2-3b in bfloat16" in out and "requests of 4096" in out and "114688 bytes a token" in out
+    assert main(["plan", "--preset", "llama3.1-70b", "--dtype", "float32"]) == 1
+    assert "does not fit" in capsys.readouterr().err

@@ -74,6 +74,8 @@ def test_greedy_generation_through_the_entry_point(case, dtype):
             assert out.tokens == plain.greedy_generate(case["cfg"], case["state"][dtype], prompt, n, torch.float64)
     m = engine.metrics()
     assert m["finished"] == len(outs) and m["kv_blocks_live"] == 0 and m["graph_replays"] > 0
+    last = engine.last_step          # the record of the last step: a decode of the requests still running
+    assert last["decode_only"] and last["tokens"] == last["seqs"] == last["rows"] >= 1 and last["us"] > 0
     if case["name"] == "B":
         assert m["prefill_tokens_reused"] > 0, "the shared 24-token prefix was never found in the cache"
 
