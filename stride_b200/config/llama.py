@@ -129,6 +129,13 @@ class LlamaConfig:
             d["attention_bias"] = any(n.endswith(".self_attn.q_proj.bias") for n in tensor_names)
         return d
 
+    def with_max_positions(self, count: int) -> "LlamaConfig":
+        """The same model with position tables for ``count`` positions. The rotation is defined for every
+        position (its angles do not depend on ``max_position_embeddings``, which only sizes the table), so a
+        tool that feeds given tokens may go on past the length the checkpoint names."""
+        import dataclasses
+        return dataclasses.replace(self, max_position_embeddings=int(count))
+
     def validate(self) -> None:
         if self.num_attention_heads % self.num_key_value_heads:
             raise ConfigError(f"{self.num_attention_heads} query heads do not divide evenly into "

@@ -27,9 +27,15 @@ def build_model(config, source, dtype: str, device="cuda", token_capacity: int =
     return model
 
 
-def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda", token_capacity: int = 2048, row_capacity: int = 256):
+def load_model(model_dir: str, dtype: str = "bfloat16", device="cuda", token_capacity: int = 2048, row_capacity: int = 256,
+               min_positions: int = 0):
+    """``min_positions``: position tables for at least this many positions, where the configuration can give them
+    (``with_max_positions``), even if the checkpoint names a shorter length."""
     source = SafetensorsSource(model_dir)
     config = load_config(model_dir, tensor_names=source.names())
+    spec_positions = getattr(config, "max_position_embeddings", None)
+    if min_positions and spec_positions is not None and spec_positions < min_positions and hasattr(config, "with_max_positions"):
+        config = config.with_max_positions(min_positions)
     return config, build_model(config, source, dtype, device, token_capacity, row_capacity)
 
 

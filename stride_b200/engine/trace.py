@@ -30,7 +30,9 @@ class TraceSession:
         self.block_size = block_size
         capacity = -(-max_tokens // block_size) * block_size
         if model is None:
-            config, model = load_model(model_dir, dtype, device, token_capacity=capacity, row_capacity=min(capacity, 256))
+            # A trace feeds given tokens: it may run past the length that the checkpoint names, as far as the pool reaches.
+            config, model = load_model(model_dir, dtype, device, token_capacity=capacity, row_capacity=min(capacity, 256),
+                                       min_positions=capacity)
         self.config, self.model = config, model
         plan = CachePlan(block_size, capacity // block_size, max_requests)
         self.device_cache, self.cache = attach_cache(model, plan, prefix_caching=False)

@@ -180,3 +180,23 @@ def test_the_trace_run_program(case, dtype, tmp_path):
         for r, key in enumerate(rows[s["step"]]):
             got[key] = torch.from_numpy(data[r].copy())
     check(got, case["want"][dtype], dtype, "bin/trace_run")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_trace_may_run_past_the_length_that_the_checkpoint_names(tmp_models, dtype):
+    """The rotation is defined for every position; ``max_position_embeddings`` only sizes the table. A replay of
+    300 given tokens through a model that names 256 positions gives the plain logits at every position."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from stride_b200.engine.trace import TraceSession
+    cfg = TINY["A"]
+    assert cfg["max_position_embeddings"] == 256
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = write_model_dir(str(tmp_models / f"past_the_end_{dtype}"), cfg, seeded_state(cfg, 91, std=0.05), stored)
+    _, state = read_model_dir(folder)
+    requests = {"long": seeded_tokens(300, cfg["vocab_size"], 17)}
+    want = {"long": plain.forward(cfg, state, requests["long"], torch.float64)}
+    for steps in (modes.whole(requests), modes.tail_one_by_one(requests, tail=60)):
+        session = TraceSession(folder, dtype, max_tokens=modes.peak_tokens(steps), block_size=16)
+        assert session.model.spec.max_positions >= 300
+        check(replay(session, steps), want, dtype, "past max_position_embeddings")
