@@ -254,7 +254,6 @@ def run_ours(args) -> dict:
         e2e = {"value": round(produced / elapsed, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // args.steps,
                "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // args.steps}
-        launches += 0
         for i in ids:
             engine.cancel(i)
 

@@ -109,9 +109,24 @@ def cmd_random_model(args) -> int:
     return 0
 
 
+def add_replay_options(p: argparse.ArgumentParser) -> None:
+    """The options of trace replay; ``bin/trace_run`` and the ``replay`` command share them."""
+    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    p.add_argument("--max-tokens", type=int, required=True,
+                   help="most tokens that live requests hold at any time (each rounded up to a multiple of 64)")
+    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    p.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+
+
 def cmd_replay(args) -> int:
+    """Reads steps from standard input, one JSON object a line, runs each through a ``TraceSession`` and writes
+    ``<out>/<step>.f32`` (little-endian float32 [wanted, vocab]) for every step that wants logits; prints
+    ``done <step>`` after every step."""
     import os
 
+    print("[trace_run] loading the engine", file=sys.stderr, flush=True)
     import numpy as np
 
     from .engine.trace import TraceSession
@@ -119,8 +134,10 @@ def cmd_replay(args) -> int:
     os.makedirs(args.out, exist_ok=True)
     session = TraceSession(args.model, dtype=args.dtype, max_tokens=args.max_tokens, block_size=args.block_size,
                            max_requests=args.max_requests)
+    print("[trace_run] ready", file=sys.stderr, flush=True)
     for line in sys.stdin:
-        if not line.strip():
+        line = line.strip()
+        if not line:
             continue
         step = json.loads(line)
         logits = session.run_step(step)
@@ -196,12 +213,7 @@ def main(argv=None) -> int:
     r.set_defaults(run=cmd_random_model)
 
     t = sub.add_parser("replay", help="feed a trace of token ids step by step and write logits (see bin/trace_run)")
-    t.add_argument("--model", required=True)
-    t.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    t.add_argument("--out", required=True)
-    t.add_argument("--max-tokens", type=int, required=True)
-    t.add_argument("--block-size", type=int, default=16)
-    t.add_argument("--max-requests", type=int, default=8)
+    add_replay_options(t)
     t.set_defaults(run=cmd_replay)
 
     pl = sub.add_parser("plan", help="what fits: weights, activation reserve and cache pages on one device (no GPU needed)")
