@@ -99,10 +99,13 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------ shapes
-def bench_config(layers: int | None):
+SHAPES = {"llama3.1-8b": "Llama-3.1-8B", "llama3.2-3b": "Llama-3.2-3B", "llama3.1-70b": "Llama-3.1-70B"}
+
+
+def bench_config(layers: int | None, shape: str = "llama3.1-8b"):
     from stride_b200.config import config_from_dict, preset
 
-    d = preset("llama3.1-8b")
+    d = preset(shape)
     full_layers = d["num_hidden_layers"]
     if layers:
         d["num_hidden_layers"] = layers
@@ -171,7 +174,7 @@ def run_ours(args) -> dict:
     from stride_b200.csrc import ops
 
     pk = peaks()
-    cfg, full_layers = bench_config(args.layers)
+    cfg, full_layers = bench_config(args.layers, args.shape)
     batch, context, prompt_len = args.batch, args.context, 2048
     page = 16
     need_tokens = max(64 * (context + 64), batch * (context + 1024)) + 4096
@@ -258,12 +261,12 @@ def run_ours(args) -> dict:
             engine.cancel(i)
 
     return {
-        "metric": "Llama-3.1-8B decode tok/s at batch 8, context 8192 (bf16, one B200)",
+        "metric": f"{SHAPES[args.shape]} decode tok/s at batch {batch}, context {context} (bf16, one B200)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0, 0.02), uniform token ids, random cache contents)",
         "impl": "ours",
-        "config": {"model": "llama-3.1-8b-shape", "layers": cfg.num_hidden_layers, "layers_of_named_config": full_layers,
+        "config": {"model": f"{SHAPES[args.shape].lower()}-shape", "layers": cfg.num_hidden_layers, "layers_of_named_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": batch, "seq_len": context, "page_size": page, "prefill_tokens": prompt_len,
@@ -284,7 +287,7 @@ def run_profile(args) -> dict:
 
     from stride_b200 import Engine
 
-    cfg, full_layers = bench_config(args.layers)
+    cfg, full_layers = bench_config(args.layers, args.shape)
     batch, context = args.batch, args.context
     engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=16,
                     num_blocks=(batch * (context + 64) + 4096) // 16, max_batch_tokens=2048, max_batch_seqs=64,
@@ -394,6 +397,8 @@ def main(argv=None) -> int:
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=8192)
+    p.add_argument("--shape", default="llama3.1-8b", choices=sorted(SHAPES),
+                   help="layer sizes of another named model (the headline is the default)")
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (reported in config)")
     p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
