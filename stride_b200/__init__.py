@@ -12,6 +12,7 @@ __version__ = "0.1.0"
 _LAZY = {
     "Engine": ("stride_b200.engine", "Engine"),
     "RequestOutput": ("stride_b200.engine", "RequestOutput"),
+    "EngineBusy": ("stride_b200.engine", "EngineBusy"),
     "TraceSession": ("stride_b200.engine", "TraceSession"),
     "write_random_model": ("stride_b200.engine", "write_random_model"),
     "random_model": ("stride_b200.engine", "random_model"),

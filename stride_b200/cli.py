@@ -33,6 +33,7 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget per step")
     p.add_argument("--max-batch-seqs", type=int, default=256, help="sequence budget per step")
     p.add_argument("--max-model-len", type=int, default=8192, help="longest prompt plus completion accepted")
+    p.add_argument("--max-queued", type=int, default=1024, help="requests that may wait for admission before more are refused")
     p.add_argument("--watermark", type=float, default=0.01, help="share of pages held back from admission")
     p.add_argument("--no-chunked-prefill", action="store_true")
     p.add_argument("--no-prefix-caching", action="store_true")
@@ -57,7 +58,8 @@ def _engine(args):
 
     options = dict(dtype=args.dtype, block_size=args.block_size, num_blocks=args.num_blocks,
                    activation_reserve=args.activation_reserve, max_batch_tokens=args.max_batch_tokens,
-                   max_batch_seqs=args.max_batch_seqs, max_model_len=args.max_model_len, watermark=args.watermark,
+                   max_batch_seqs=args.max_batch_seqs, max_model_len=args.max_model_len, max_queued=args.max_queued,
+                   watermark=args.watermark,
                    chunked_prefill=not args.no_chunked_prefill, prefix_caching=not args.no_prefix_caching,
                    cuda_graphs=not args.no_cuda_graphs, check_invariants=args.check_invariants)
     if args.model:

@@ -2,7 +2,7 @@
 of the reference's command lines (python/stride_worker/worker.py:252-280:
 ``--dtype``, ``--block-size``, ``--num-blocks``, ``--activation-reserve``;
 crates/stride-server/src/main.rs:86-107: ``--max-batch-tokens``,
-``--max-batch-seqs``, ``--max-model-len``; scheduler watermark and chunked
+``--max-batch-seqs``, ``--max-model-len``, ``--max-queued``; scheduler watermark and chunked
 prefill from crates/stride-sched/src/lib.rs:31-55)."""
 
 from __future__ import annotations
@@ -24,6 +24,7 @@ class EngineConfig:
     max_batch_tokens: int = 2048
     max_batch_seqs: int = 256
     max_model_len: int = 8192
+    max_queued: int = 1024                   # requests that may wait for admission before add_request refuses more
     watermark: float = 0.01
     chunked_prefill: bool = True
     prefix_caching: bool = True
@@ -42,6 +43,8 @@ class EngineConfig:
             raise ValueError("activation_reserve must be in [0, 1)")
         if self.max_batch_tokens <= 0 or self.max_batch_seqs <= 0 or self.max_model_len <= 1:
             raise ValueError("batch and length limits must be positive")
+        if self.max_queued <= 0:
+            raise ValueError("max_queued must be positive")
 
     @property
     def torch_dtype(self) -> torch.dtype:

@@ -318,25 +318,33 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
     }
 }
 
-// silu_mul_kernel with 16-byte accesses (block % V == 0).
+// silu_mul_kernel with 16-byte accesses (block % V == 0): one pack per thread and no loop, the form that streams
+// fastest here (several packs per thread, a grid-stride apart, measured 25 to 80 % slower).
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int block, size_t packs) {
     pdl_trigger();
     pdl_wait();
     constexpr int V = Pack<T>::V;
     const int per_row = inter / V;
-    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < packs;
-         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t t = idx / per_row;
-        const int i = static_cast<int>(idx - t * per_row) * V;
-        Pack<T> g, u;
-        const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
-        g.load(in + at);
-        u.load(in + at + block);
+    const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+    if (idx >= packs) return;
+    const size_t t = idx / per_row;
+    const int i = static_cast<int>(idx - t * per_row) * V;
+    Pack<T> g, u;
+    const size_t at = t * 2 * inter + static_cast<size_t>(i / block) * 2 * block + i % block;
+    g.load(in + at);
+    u.load(in + at + block);
 #pragma unroll
-        for (int j = 0; j < V; ++j) g.v[j] = (g.v[j] / (1.f + expf(-g.v[j]))) * u.v[j];
-        g.store(out + t * inter + i);
+    for (int j = 0; j < V; ++j) {
+        if constexpr (sizeof(T) == 2) {
+            // bfloat16: the hardware exponential and reciprocal (a few units in the last place of float32, far below
+            // the rounding of the result to bfloat16) take a tenth off the kernel; float32 stays exact
+            g.v[j] = __fmul_rn(__fmul_rn(g.v[j], __frcp_rn(1.f + __expf(-g.v[j]))), u.v[j]);
+        } else {
+            g.v[j] = (g.v[j] / (1.f + expf(-g.v[j]))) * u.v[j];
+        }
     }
+    g.store(out + t * inter + i);
 }
 
 // embed_gather_kernel with 16-byte reads of the table (hidden % V == 0).
@@ -507,11 +515,12 @@ int stride_silu_mul(const void* in, void* out, int tokens, int inter, int block,
         const int vec = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
         if (bits % 16 == 0 && block % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
             const size_t packs = total / vec;
-            const unsigned vblocks = static_cast<unsigned>(std::min<size_t>((packs + 255) / 256, 148 * 16));
+            if ((packs + 127) / 128 > 0x7fffffffull) return STRIDE_UNSUPPORTED;
+            const unsigned vblocks = static_cast<unsigned>((packs + 127) / 128);
             if (dtype == STRIDE_DTYPE_F32)
-                stride::launch(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, block, packs);
+                stride::launch(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(128), 0, stream, static_cast<const float*>(in), static_cast<float*>(out), inter, block, packs);
             else
-                stride::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, block, packs);
+                stride::launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), inter, block, packs);
             return STRIDE_LAUNCH_STATUS();
         }
     }

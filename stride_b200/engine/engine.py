@@ -35,6 +35,10 @@ from .runner import ModelRunner
 _NVTX = os.environ.get("STRIDE_B200_NVTX", "0") == "1"      # named ranges around every step, for a timeline profiler
 
 
+class EngineBusy(RuntimeError):
+    """``add_request`` refuses: too many requests wait for admission already."""
+
+
 @dataclass
 class RequestOutput:
     request_id: int
@@ -116,6 +120,9 @@ class Engine:
         """Queues one request; returns its id. Raises ValueError when the
         sampling parameters are invalid, the prompt is empty or too long, or a
         token lies outside the vocabulary."""
+        if self.scheduler.num_waiting >= self.cfg.max_queued:
+            # the reference's engine tells its API layer to back off at this point (crates/stride-engine/src/lib.rs:68-70)
+            raise EngineBusy(f"{self.scheduler.num_waiting} requests are waiting for admission (max_queued {self.cfg.max_queued})")
         params = params if params is not None else self._rt.SamplingParams()
         tokens = [int(t) for t in tokens]
         for t in tokens:

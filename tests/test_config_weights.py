@@ -95,7 +95,8 @@ def test_parameter_and_cache_arithmetic_of_the_named_shapes():
 
 def test_engine_config_is_validated():
     assert EngineConfig().block_size == 16 and EngineConfig().max_batch_tokens == 2048
-    for bad in ({"dtype": "float16"}, {"block_size": 0}, {"activation_reserve": 1.0}, {"max_batch_seqs": 0}):
+    assert EngineConfig().max_queued == 1024 and EngineConfig().max_batch_seqs == 256 and EngineConfig().max_model_len == 8192
+    for bad in ({"dtype": "float16"}, {"block_size": 0}, {"activation_reserve": 1.0}, {"max_batch_seqs": 0}, {"max_queued": 0}):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
 

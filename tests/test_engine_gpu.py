@@ -114,6 +114,22 @@ def test_a_long_prompt_alone_is_prefilled_in_full_portions_from_a_graph(case, dt
     assert engine.runner.graph_replays > replays
 
 
+def test_add_request_refuses_more_than_max_queued_waiting_requests(case):
+    from stride_b200 import EngineBusy, SamplingParams
+    engine = engine_for(case, "float32", max_queued=2)
+    params = SamplingParams(temperature=0.0, max_tokens=3)
+    first = [engine.add_request(p, params) for p in case["prompts"][:2]]
+    with pytest.raises(EngineBusy, match="max_queued 2"):
+        engine.add_request(case["prompts"][2], params)
+    engine.step()                                   # both are admitted: nothing waits any more
+    third = engine.add_request(case["prompts"][2], params)
+    while engine.has_unfinished():
+        engine.step()
+    for rid, prompt in zip(first + [third], case["prompts"][:3]):
+        out = engine.output(rid)
+        assert out.finished and out.tokens == plain.greedy_generate(case["cfg"], case["state"]["float32"], prompt, 3, torch.float64)
+
+
 def test_stop_rules(case):
     from stride_b200 import SamplingParams
     prompt = case["prompts"][-1]
