@@ -1,9 +1,10 @@
 // Python bindings of the host runtime: page pools, cache manager, step batches,
-// sampler and scheduler. No CUDA here: this module builds and runs without a GPU.
+// sampler, scheduler and the host side of the engine's step. No CUDA here: this module builds and runs without a GPU.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include "engine_core.hpp"
 #include "scheduler.hpp"
 
 namespace py = pybind11;
@@ -49,6 +50,7 @@ PYBIND11_MODULE(_runtime, m) {
     py::register_exception<InvariantError>(m, "InvariantError");
     py::register_exception<OutOfPages>(m, "OutOfPages");
     py::register_exception<AdmissionError>(m, "AdmissionError", PyExc_ValueError);
+    py::register_exception<EngineBusy>(m, "EngineBusy", PyExc_RuntimeError);
 
     m.def("tenant_root", &prefix_hash::tenant_root);
     m.def("prefix_chain", [](const std::string& tenant, const std::vector<TokenId>& tokens, size_t page_size) {
@@ -325,4 +327,52 @@ PYBIND11_MODULE(_runtime, m) {
             d["prefill_reuse_rate"] = mt.prefill_reuse_rate();
             return d;
         });
+
+    py::class_<StepEvent>(m, "StepEvent")
+        .def_readonly("request", &StepEvent::request)
+        .def_property_readonly("token", [](const StepEvent& e) -> py::object { return e.has_token ? py::cast(e.token) : py::none(); })
+        .def_readonly("reason", &StepEvent::reason);
+
+    py::class_<RequestRecord>(m, "RequestRecord")
+        .def_readonly("request", &RequestRecord::request)
+        .def_readonly("seq", &RequestRecord::seq)
+        .def_readonly("prompt_len", &RequestRecord::prompt_len)
+        .def_readonly("seed", &RequestRecord::seed)
+        .def_readonly("tokens", &RequestRecord::tokens)
+        .def_readonly("finished", &RequestRecord::finished)
+        .def_readonly("reason", &RequestRecord::reason)
+        .def_readonly("cached_prefix_len", &RequestRecord::cached_prefix_len)
+        .def_readonly("ttft_us", &RequestRecord::ttft_us)
+        .def_readonly("mean_itl_us", &RequestRecord::mean_itl_us);
+
+    py::class_<EngineCore>(m, "EngineCore")
+        .def(py::init<Scheduler*, int32_t, std::vector<int32_t>, uint64_t, size_t, size_t>(), py::arg("scheduler"), py::arg("eos"),
+             py::arg("extra_stops"), py::arg("base_seed"), py::arg("max_queued"), py::arg("vocab"), py::keep_alive<1, 2>())
+        .def("add_request", &EngineCore::add_request, py::arg("prompt"), py::arg("params"), py::arg("tenant") = "default",
+             py::arg("klass") = ServiceClass::Interactive, py::arg("now") = 0)
+        .def("has_unfinished", &EngineCore::has_unfinished)
+        .def_property_readonly("num_live", &EngineCore::num_live)
+        .def("record", &EngineCore::record, py::return_value_policy::copy)
+        .def("forget", &EngineCore::forget)
+        .def("cancel", &EngineCore::cancel)
+        .def("begin_step", &EngineCore::begin_step, py::arg("now"))
+        .def("batch", [](EngineCore& c) { return &c.batch(); }, py::return_value_policy::reference_internal)
+        .def("rows", &EngineCore::rows)
+        .def("prepare_sampling",
+             [](EngineCore& c, py::array_t<float, py::array::c_style> temperature, py::array_t<float, py::array::c_style> uniform,
+                py::array_t<int32_t, py::array::c_style> suppress) {
+                 size_t cap = std::min({size_t(temperature.size()), size_t(uniform.size()), size_t(suppress.size())});
+                 return c.prepare_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
+             })
+        .def("finish_step",
+             [](EngineCore& c, py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens, std::vector<int32_t> ranked,
+                py::object ranked_logits, Tick now) {
+                 if (ranked.empty()) return c.finish_step(tokens.data(), size_t(tokens.size()), ranked, nullptr, 0, now);
+                 auto rows = ranked_logits.cast<py::array_t<float, py::array::c_style | py::array::forcecast>>();
+                 if (rows.ndim() != 2 || size_t(rows.shape(0)) != ranked.size())
+                     throw std::invalid_argument("ranked_logits must be [ranked rows, vocab]");
+                 return c.finish_step(tokens.data(), size_t(tokens.size()), ranked, rows.data(), size_t(rows.shape(1)), now);
+             },
+             py::arg("tokens"), py::arg("ranked") = std::vector<int32_t>{}, py::arg("ranked_logits") = py::none(), py::arg("now") = 0)
+        .def("abandon_step", &EngineCore::abandon_step);
 }

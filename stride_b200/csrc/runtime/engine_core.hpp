@@ -1,0 +1,239 @@
+// The host side of one engine step, without the device: what runs before the
+// kernels are launched (scheduling, the step's batch, the parameters of the
+// device sampler) and what runs after the sampled tokens are back (stop rules,
+// feeding tokens to the scheduler, retiring). The reference's engine loop does
+// the same between its scheduler and its executor
+// (crates/stride-engine/src/lib.rs:263-297 admit, :299-414 step, :433-457
+// retire); here the executor is the caller, who launches the step function and
+// the sampling kernel between begin_step() and finish_step().
+//
+// Per request the core keeps its sampler (seeded base + request id when the
+// request brings no seed, lib.rs:278-287), the tokens it has produced and, once
+// it has ended, why. Greedy and plain-temperature rows are drawn on the device
+// from the arrays that prepare_sampling() fills; rows that need a ranking
+// (top-k, top-p) are drawn here from their logits, which the caller brings.
+#pragma once
+
+#include <map>
+
+#include "scheduler.hpp"
+
+namespace stride {
+
+struct EngineBusy : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+struct StepEvent {
+    int64_t request = 0;
+    bool has_token = false;
+    TokenId token = 0;
+    FinishReason reason = FinishReason::None;      // None: the request goes on
+};
+
+struct RequestRecord {
+    int64_t request = 0;
+    SeqId seq = 0;
+    size_t prompt_len = 0;
+    uint64_t seed = 0;
+    std::vector<TokenId> tokens;
+    bool finished = false;
+    FinishReason reason = FinishReason::None;
+    size_t cached_prefix_len = 0;
+    std::optional<Tick> ttft_us;
+    std::optional<double> mean_itl_us;
+};
+
+class EngineCore {
+public:
+    EngineCore(Scheduler* scheduler, int32_t eos, std::vector<int32_t> extra_stops, uint64_t base_seed, size_t max_queued,
+               size_t vocab)
+        : sched_(scheduler), eos_(eos), extra_stops_(std::move(extra_stops)), base_seed_(base_seed), max_queued_(max_queued),
+          vocab_(vocab) {
+        if (max_queued_ == 0) throw std::invalid_argument("max_queued must be positive");
+    }
+
+    // Admits a request and returns its id. Throws EngineBusy when too many requests wait already, AdmissionError
+    // (from the scheduler) for a request that can never run, std::invalid_argument for bad parameters or tokens.
+    int64_t add_request(std::vector<TokenId> prompt, SamplingParams params, const std::string& tenant, ServiceClass klass,
+                        Tick now) {
+        if (sched_->num_waiting() >= max_queued_)
+            throw EngineBusy(std::to_string(sched_->num_waiting()) + " requests are waiting for admission (max_queued " +
+                             std::to_string(max_queued_) + ")");
+        for (TokenId t : prompt)
+            if (t < 0 || size_t(t) >= vocab_)
+                throw std::invalid_argument("token " + std::to_string(t) + " lies outside the vocabulary of " + std::to_string(vocab_));
+        for (int32_t s : extra_stops_)
+            if (std::find(params.stop_tokens.begin(), params.stop_tokens.end(), s) == params.stop_tokens.end())
+                params.stop_tokens.push_back(s);
+        int64_t rid = next_request_;
+        SeqId seq = sched_->admit(rid, tenant, prompt, params, klass, now);
+        ++next_request_;
+        Live live{rid, Sampler(params, eos_, base_seed_ + uint64_t(rid))};
+        RequestRecord rec;
+        rec.request = rid;
+        rec.seq = seq;
+        rec.prompt_len = prompt.size();
+        rec.seed = live.sampler.effective_seed();
+        records_.emplace(rid, std::move(rec));
+        live_.emplace(seq, std::move(live));
+        return rid;
+    }
+
+    bool has_unfinished() const { return !live_.empty(); }
+    size_t num_live() const { return live_.size(); }
+
+    const RequestRecord& record(int64_t request) const {
+        auto it = records_.find(request);
+        if (it == records_.end()) throw std::out_of_range("unknown request " + std::to_string(request));
+        return it->second;
+    }
+    // Drops the record of a finished request (its output has been handed over).
+    void forget(int64_t request) {
+        auto it = records_.find(request);
+        if (it != records_.end() && it->second.finished) records_.erase(it);
+    }
+
+    std::vector<StepEvent> cancel(int64_t request) {
+        std::vector<StepEvent> events;
+        for (auto& f : sched_->cancel(request)) {
+            events.push_back(StepEvent{f.request, false, 0, FinishReason::Cancelled});
+            retire(f.seq, FinishReason::Cancelled, &f);
+        }
+        return events;
+    }
+
+    // ---- before the launch. False: nothing can run at this tick (the caller advances its clock).
+    bool begin_step(Tick now) {
+        if (in_step_) throw std::logic_error("begin_step while a step is open");
+        scheduled_ = sched_->step(now);
+        if (scheduled_.empty()) return false;
+        batch_ = std::make_unique<StepBatch>(sched_->cache());
+        for (auto& item : sched_->work_items(scheduled_)) batch_->add(item);
+        rows_ = batch_->row_requests();
+        in_step_ = true;
+        return true;
+    }
+
+    const StepBatch& batch() const {
+        if (!batch_) throw std::logic_error("no step is open");
+        return *batch_;
+    }
+    const std::vector<RequestKey>& rows() const { return rows_; }
+
+    // Fills, per wanted row, what the device sampler reads: the temperature (0: first maximum), a uniform number
+    // from the request's generator (0 for greedy rows, which draw none) and the token to suppress (-1: none).
+    // Returns the rows that need a ranking and are therefore drawn by finish_step from their logits; their
+    // device parameters are those of a greedy row.
+    std::vector<int32_t> prepare_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity) {
+        if (!in_step_) throw std::logic_error("no step is open");
+        if (rows_.size() > capacity) throw std::invalid_argument("more rows than the sampling arrays hold");
+        std::vector<int32_t> ranked;
+        for (size_t r = 0; r < rows_.size(); ++r) {
+            Live& live = live_.at(rows_[r]);
+            const SamplingParams& p = live.sampler.params();
+            size_t generated = records_.at(live.request).tokens.size();
+            suppress[r] = live.sampler.suppressed_token(generated);
+            if (p.needs_ranking()) {
+                ranked.push_back(int32_t(r));
+                temperature[r] = 0.f;
+                uniform[r] = 0.f;
+            } else if (p.is_greedy()) {
+                temperature[r] = 0.f;
+                uniform[r] = 0.f;
+            } else {
+                temperature[r] = p.temperature;
+                uniform[r] = live.sampler.next_uniform();
+            }
+        }
+        return ranked;
+    }
+
+    // ---- after the launch. `tokens`: one per wanted row, from the device. `ranked_logits`: [ranked rows][vocab]
+    // in the order that prepare_sampling returned. The window groups give back passed pages, every token goes
+    // through the stop rules and on to the scheduler, and requests that end are retired.
+    std::vector<StepEvent> finish_step(const int32_t* tokens, size_t count, const std::vector<int32_t>& ranked,
+                                       const float* ranked_logits, size_t vocab, Tick now) {
+        if (!in_step_) throw std::logic_error("no step is open");
+        if (count != rows_.size()) throw std::invalid_argument("one token per wanted row is needed");
+        in_step_ = false;
+        sched_->after_step(scheduled_);
+        std::vector<TokenId> drawn(tokens, tokens + count);
+        for (size_t i = 0; i < ranked.size(); ++i) {
+            size_t r = size_t(ranked[i]);
+            if (r >= count || ranked_logits == nullptr) throw std::invalid_argument("ranked rows without their logits");
+            Live& live = live_.at(rows_[r]);
+            drawn[r] = live.sampler.sample(ranked_logits + i * vocab, vocab, records_.at(live.request).tokens.size());
+        }
+        std::vector<StepEvent> events;
+        std::vector<std::pair<SeqId, TokenId>> sampled;
+        std::vector<SeqId> stopped;
+        for (size_t r = 0; r < count; ++r) {
+            auto it = live_.find(rows_[r]);
+            if (it == live_.end()) continue;
+            Live& live = it->second;
+            if (live.sampler.is_stop(drawn[r])) {
+                stopped.push_back(rows_[r]);        // the stop token itself is not appended (lib.rs:393-397)
+            } else {
+                sampled.emplace_back(rows_[r], drawn[r]);
+                records_.at(live.request).tokens.push_back(drawn[r]);
+                events.push_back(StepEvent{live.request, true, drawn[r], FinishReason::None});
+            }
+        }
+        std::vector<Finished> at_limit = sched_->on_tokens(sampled, now);
+        for (SeqId seq : stopped) {
+            auto f = sched_->stop(seq);
+            events.push_back(StepEvent{live_.at(seq).request, false, 0, FinishReason::Stop});
+            retire(seq, FinishReason::Stop, f ? &*f : nullptr);
+        }
+        for (auto& f : at_limit) {
+            events.push_back(StepEvent{f.request, false, 0, FinishReason::Length});
+            retire(f.seq, FinishReason::Length, &f);
+        }
+        batch_.reset();
+        return events;
+    }
+
+    // Gives up an open step whose launch failed: nothing was sampled. Fatal for the requests in it, as in the
+    // reference, whose scheduler has already advanced them; the caller is expected to stop.
+    void abandon_step() {
+        in_step_ = false;
+        batch_.reset();
+    }
+
+private:
+    struct Live {
+        int64_t request;
+        Sampler sampler;
+    };
+
+    void retire(SeqId seq, FinishReason reason, const Finished* f) {
+        auto it = live_.find(seq);
+        if (it == live_.end()) return;
+        RequestRecord& rec = records_.at(it->second.request);
+        rec.finished = true;
+        rec.reason = reason;
+        if (f) {
+            rec.cached_prefix_len = f->cached_prefix_len;
+            rec.ttft_us = f->ttft_us;
+            rec.mean_itl_us = f->mean_itl_us;
+        }
+        live_.erase(it);
+        sched_->forget(seq);
+    }
+
+    Scheduler* sched_;
+    int32_t eos_;
+    std::vector<int32_t> extra_stops_;
+    uint64_t base_seed_;
+    size_t max_queued_, vocab_;
+    int64_t next_request_ = 1;
+    std::map<SeqId, Live> live_;
+    std::map<int64_t, RequestRecord> records_;
+    ScheduledBatch scheduled_;
+    std::unique_ptr<StepBatch> batch_;
+    std::vector<RequestKey> rows_;
+    bool in_step_ = false;
+};
+
+}  // namespace stride
