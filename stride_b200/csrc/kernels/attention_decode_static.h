@@ -20,11 +20,16 @@
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress) and raises the kernel's shared-memory limit. Make
 //     that first call outside any stream capture; later calls only launch.
-//   * All calls on a device share the one array. The array keeps whatever the
-//     last call left in it; nothing in it has to be zero, because every value a
-//     call reads was written earlier in the same call. Two calls that overlap
-//     on the GPU (different streams, or one device driven from two threads)
-//     overwrite each other's partial results: run them one after the other.
+//   * All calls on a device share the one array, and it keeps whatever the last
+//     call left in it. Only the ticket counters at its start (one per token and
+//     key head, by which the last split of a group finds out that it is the
+//     last) have to be zero when a call begins: they are zero when the library
+//     is loaded, and the CTA that draws the last ticket of a group sets it back
+//     to zero, so every completed call leaves them cleared for the next one.
+//     Everything else a call reads was written earlier in the same call. Two
+//     calls that overlap on the GPU (different streams, or one device driven
+//     from two threads) overwrite each other's partial results and tickets:
+//     run them one after the other.
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
 //
 // Inputs and outputs are the caller's, with the meanings of
