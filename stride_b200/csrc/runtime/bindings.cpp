@@ -309,6 +309,8 @@ PYBIND11_MODULE(_runtime, m) {
              },
              py::keep_alive<0, 1>())
         .def("after_step", &Scheduler::after_step)
+        .def("reserve_chain", &Scheduler::reserve_chain)
+        .def("adopt_chain", &Scheduler::adopt_chain)
         .def("on_tokens", &Scheduler::on_tokens, py::arg("outputs"), py::arg("now"))
         .def("stop", &Scheduler::stop)
         .def("cancel", &Scheduler::cancel)
@@ -374,5 +376,17 @@ PYBIND11_MODULE(_runtime, m) {
                  return c.finish_step(tokens.data(), size_t(tokens.size()), ranked, rows.data(), size_t(rows.shape(1)), now);
              },
              py::arg("tokens"), py::arg("ranked") = std::vector<int32_t>{}, py::arg("ranked_logits") = py::none(), py::arg("now") = 0)
-        .def("abandon_step", &EngineCore::abandon_step);
+        .def("abandon_step", &EngineCore::abandon_step)
+        .def("launched_ahead", &EngineCore::launched_ahead)
+        .def_property_readonly("chained_steps", &EngineCore::chained_steps)
+        .def_property_readonly("dropped_chains", &EngineCore::dropped_chains)
+        .def("chain_step", &EngineCore::chain_step)
+        .def("has_next", &EngineCore::has_next)
+        .def("next_batch", [](EngineCore& c) { return &c.next_batch(); }, py::return_value_policy::reference_internal)
+        .def("prepare_next_sampling",
+             [](EngineCore& c, py::array_t<float, py::array::c_style> temperature, py::array_t<float, py::array::c_style> uniform,
+                py::array_t<int32_t, py::array::c_style> suppress) {
+                 size_t cap = std::min({size_t(temperature.size()), size_t(uniform.size()), size_t(suppress.size())});
+                 c.prepare_next_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
+             });
 }

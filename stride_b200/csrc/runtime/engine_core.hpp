@@ -106,6 +106,27 @@ public:
     // ---- before the launch. False: nothing can run at this tick (the caller advances its clock).
     bool begin_step(Tick now) {
         if (in_step_) throw std::logic_error("begin_step while a step is open");
+        launched_ = false;
+        if (next_batch_) {
+            // The step was launched ahead (chain_step): take it over instead of scheduling. Requests of it that
+            // have ended since keep their rows, which finish_step passes over. If all of them have ended, the
+            // launched step is of no use to anybody: it is dropped (its results are never read) and the step is
+            // scheduled in the ordinary way.
+            ScheduledBatch adopted = sched_->adopt_chain(next_rows_);
+            if (!adopted.decode.empty()) {
+                scheduled_ = std::move(adopted);
+                batch_ = std::move(next_batch_);
+                rows_ = std::move(next_rows_);
+                next_rows_.clear();
+                ++chained_steps_;
+                launched_ = true;
+                in_step_ = true;
+                return true;
+            }
+            next_batch_.reset();
+            next_rows_.clear();
+            ++dropped_chains_;
+        }
         scheduled_ = sched_->step(now);
         if (scheduled_.empty()) return false;
         batch_ = std::make_unique<StepBatch>(sched_->cache());
@@ -113,6 +134,49 @@ public:
         rows_ = batch_->row_requests();
         in_step_ = true;
         return true;
+    }
+
+    // True when the open step was launched ahead by chain_step(): the caller only waits for its tokens.
+    bool launched_ahead() const { return in_step_ && launched_; }
+    uint64_t chained_steps() const { return chained_steps_; }
+    uint64_t dropped_chains() const { return dropped_chains_; }
+
+    // ---- between the launch of the open step and the arrival of its tokens: the step after it, launched ahead.
+    // Possible when the open step holds single decoded tokens only, every one of its rows is drawn on the device
+    // (so that the tokens can travel to the next step without the host), and the scheduler can promise the same
+    // requests one position further (Scheduler::reserve_chain). On success next_batch() holds the chained step: the
+    // same requests in the same order, one position on, with token ids that the caller overwrites on the device
+    // with the open step's sampled tokens (row r of the open step feeds token r of the chained one);
+    // prepare_next_sampling() fills its sampler arrays. The chained step becomes the open step at the next
+    // begin_step(). False: nothing was changed and the next step is scheduled in the ordinary way.
+    bool chain_step() {
+        if (!in_step_) throw std::logic_error("no step is open");
+        if (next_batch_) throw std::logic_error("a chained step is pending already");
+        if (!batch_->decode_only() || rows_.size() != batch_->num_seqs()) return false;
+        for (RequestKey seq : rows_) {
+            auto it = live_.find(seq);
+            if (it == live_.end() || it->second.sampler.params().needs_ranking()) return false;
+        }
+        if (scheduled_.decode != rows_) return false;      // rows of ended requests (a chained step being chained again)
+        if (!sched_->reserve_chain(scheduled_)) return false;
+        auto next = std::make_unique<StepBatch>(sched_->cache());
+        for (auto& item : batch_->items()) next->add(WorkItem{item.request, {0}, item.position + 1, {0}});
+        next_batch_ = std::move(next);
+        next_rows_ = rows_;
+        return true;
+    }
+
+    bool has_next() const { return bool(next_batch_); }
+    const StepBatch& next_batch() const {
+        if (!next_batch_) throw std::logic_error("no chained step is pending");
+        return *next_batch_;
+    }
+
+    // prepare_sampling for the chained step: every request is one token further than its record says.
+    void prepare_next_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity) {
+        if (!next_batch_) throw std::logic_error("no chained step is pending");
+        if (next_rows_.size() > capacity) throw std::invalid_argument("more rows than the sampling arrays hold");
+        fill_sampling(next_rows_, 1, temperature, uniform, suppress);
     }
 
     const StepBatch& batch() const {
@@ -128,25 +192,8 @@ public:
     std::vector<int32_t> prepare_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity) {
         if (!in_step_) throw std::logic_error("no step is open");
         if (rows_.size() > capacity) throw std::invalid_argument("more rows than the sampling arrays hold");
-        std::vector<int32_t> ranked;
-        for (size_t r = 0; r < rows_.size(); ++r) {
-            Live& live = live_.at(rows_[r]);
-            const SamplingParams& p = live.sampler.params();
-            size_t generated = records_.at(live.request).tokens.size();
-            suppress[r] = live.sampler.suppressed_token(generated);
-            if (p.needs_ranking()) {
-                ranked.push_back(int32_t(r));
-                temperature[r] = 0.f;
-                uniform[r] = 0.f;
-            } else if (p.is_greedy()) {
-                temperature[r] = 0.f;
-                uniform[r] = 0.f;
-            } else {
-                temperature[r] = p.temperature;
-                uniform[r] = live.sampler.next_uniform();
-            }
-        }
-        return ranked;
+        if (launched_) throw std::logic_error("the open step was launched ahead with its sampler arrays");
+        return fill_sampling(rows_, 0, temperature, uniform, suppress);
     }
 
     // ---- after the launch. `tokens`: one per wanted row, from the device. `ranked_logits`: [ranked rows][vocab]
@@ -199,6 +246,8 @@ public:
     void abandon_step() {
         in_step_ = false;
         batch_.reset();
+        next_batch_.reset();
+        next_rows_.clear();
     }
 
 private:
@@ -206,6 +255,30 @@ private:
         int64_t request;
         Sampler sampler;
     };
+
+    // `ahead`: tokens that the requests will have produced by then beyond what their records hold.
+    std::vector<int32_t> fill_sampling(const std::vector<RequestKey>& rows, size_t ahead, float* temperature, float* uniform,
+                                       int32_t* suppress) {
+        std::vector<int32_t> ranked;
+        for (size_t r = 0; r < rows.size(); ++r) {
+            Live& live = live_.at(rows[r]);
+            const SamplingParams& p = live.sampler.params();
+            size_t generated = records_.at(live.request).tokens.size() + ahead;
+            suppress[r] = live.sampler.suppressed_token(generated);
+            if (p.needs_ranking()) {
+                ranked.push_back(int32_t(r));
+                temperature[r] = 0.f;
+                uniform[r] = 0.f;
+            } else if (p.is_greedy()) {
+                temperature[r] = 0.f;
+                uniform[r] = 0.f;
+            } else {
+                temperature[r] = p.temperature;
+                uniform[r] = live.sampler.next_uniform();
+            }
+        }
+        return ranked;
+    }
 
     void retire(SeqId seq, FinishReason reason, const Finished* f) {
         auto it = live_.find(seq);
@@ -231,9 +304,10 @@ private:
     std::map<SeqId, Live> live_;
     std::map<int64_t, RequestRecord> records_;
     ScheduledBatch scheduled_;
-    std::unique_ptr<StepBatch> batch_;
-    std::vector<RequestKey> rows_;
-    bool in_step_ = false;
+    std::unique_ptr<StepBatch> batch_, next_batch_;
+    std::vector<RequestKey> rows_, next_rows_;
+    bool in_step_ = false, launched_ = false;
+    uint64_t chained_steps_ = 0, dropped_chains_ = 0;
 };
 
 }  // namespace stride

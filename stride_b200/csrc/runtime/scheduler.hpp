@@ -265,6 +265,43 @@ public:
         return batch;
     }
 
+    // ---- a step launched before the tokens of the step before it are known.
+    // After a step of decodes only has been scheduled (and launched), the same requests can be launched one
+    // position further right away, their next tokens travelling on the device, if nothing else could change the
+    // batch: nobody waits for admission, every running request is in the batch, none reaches max_tokens or
+    // max_model_len with the token to come, and a page for one more token each is there without taking one from
+    // anybody. What cannot be known in advance is a stop token; such a request's row in the chained step is
+    // dropped by the caller when its tokens arrive. Returns false, and reserves nothing that matters, otherwise.
+    bool reserve_chain(const ScheduledBatch& batch) {
+        if (!batch.prefill.empty() || batch.decode.empty() || !waiting_.empty()) return false;
+        if (batch.decode.size() != running_.size()) return false;
+        for (SeqId id : batch.decode) {
+            const Sequence& s = seqs_.at(id);
+            if (s.state != SeqState::Decoding || s.kv_len != s.total_len()) return false;
+            if (s.output_len() + 1 >= s.max_tokens || s.total_len() + 1 >= cfg_.max_model_len) return false;
+        }
+        for (SeqId id : batch.decode)       // pages a request gets here and does not use go back when it ends
+            if (!cache_->ensure(id, seqs_.at(id).total_len() + 1, 0)) return false;
+        return true;
+    }
+
+    // The chained step's work, once the tokens of the step before it have been fed back (on_tokens) and requests
+    // that stopped have been retired: the survivors of `chained`, each with its newest token at the next position.
+    // Counts as a step if anybody is left; the scheduler's own step() is not called for it.
+    ScheduledBatch adopt_chain(const std::vector<SeqId>& chained) {
+        ScheduledBatch batch;
+        for (SeqId id : chained) {
+            auto it = seqs_.find(id);
+            if (it == seqs_.end() || it->second.state != SeqState::Decoding) continue;
+            Sequence& s = it->second;
+            if (s.kv_len + 1 != s.total_len()) throw InvariantError("a chained request did not receive its token");
+            s.kv_len = s.total_len();
+            batch.decode.push_back(id);
+        }
+        if (!batch.decode.empty()) ++metrics_.steps;
+        return batch;
+    }
+
     // The step's work items: portions first, then decodes; logits are wanted
     // where a portion reaches the end of the context and at every decode
     // (crates/stride-engine/src/lib.rs:314-369).

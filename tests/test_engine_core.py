@@ -281,3 +281,148 @@ def test_refusals_and_misuse_are_errors():
     core.forget(a)
     with pytest.raises(IndexError):
         core.record(a)
+
+
+# --------------------------------------------------------------------------------------- steps launched ahead
+class ChainLoop(CoreLoop):
+    """The loop with the next step launched before the tokens of the open one are read. The stand-in device keeps
+    the tokens it has drawn (as the device does) and feeds them to the chained step's rows; the host reads them
+    afterwards. `launches` records, per device step, whether it was launched ahead."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.pending = None            # (tokens drawn by the step launched ahead, in row order)
+        self.launches = []
+
+    def _run_on_device(self, batch, feed):
+        """Logits and device-drawn tokens of a batch; `feed[r]`, when given, replaces the single token of item r."""
+        rows = []
+        for r, (seq, tokens, position, want) in enumerate(batch.items()):
+            history = list(self.sched.sequence(seq).tokens) if self.sched.sequence(seq) is not None else None
+            if feed is not None:
+                # the chained step: its context is what the host knew at launch time plus the token fed on the device
+                history = self._history_at_launch[seq] + [int(feed[r])]
+                assert position == len(history) - 1
+            rows += [pseudo_logits(history[:position + w + 1]) for w in want]
+        return rows
+
+    def step(self, now):
+        core = self.core
+        if not core.begin_step(now):
+            return None
+        if core.launched_ahead():
+            tokens = self.pending                       # launched and drawn already
+            self.pending = None
+            self.launches.append("ahead")
+        else:
+            batch = core.batch()
+            logits = row_logits(self.sched, batch)
+            ranked = core.prepare_sampling(self.temperature, self.uniform, self.suppress)
+            tokens = np.array([device_sampler(logits[r], float(self.temperature[r]), float(self.uniform[r]), int(self.suppress[r]))
+                               for r in range(len(logits))], dtype=np.int32)
+            self.launches.append("now")
+            if ranked:
+                ranked_logits = np.stack([logits[r] for r in ranked])
+                events = core.finish_step(tokens, ranked, ranked_logits, now)
+                return [(e.request, e.token, None if e.reason == rt.FinishReason.NotFinished else e.reason.name) for e in events]
+        # the tokens of the open step are on the device now, not yet on the host: launch the step after it
+        if core.chain_step():
+            nxt = core.next_batch()
+            self._history_at_launch = {seq: list(self.sched.sequence(seq).tokens) for seq, _t, _p, _w in nxt.items()}
+            core.prepare_next_sampling(self.temperature, self.uniform, self.suppress)
+            logits = self._run_on_device(nxt, feed=tokens)
+            self.pending = np.array([device_sampler(logits[r], float(self.temperature[r]), float(self.uniform[r]), int(self.suppress[r]))
+                                     for r in range(len(logits))], dtype=np.int32)
+        events = core.finish_step(tokens, [], None, now)
+        return [(e.request, e.token, None if e.reason == rt.FinishReason.NotFinished else e.reason.name) for e in events]
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_steps_launched_ahead_change_no_token(seed):
+    """Every request's tokens are the same with and without chained steps (the stand-in's logits depend on the
+    context alone), the cache manager's invariants hold after every step, and chains do happen."""
+    rng = random.Random(1000 + seed)
+    pages = rng.choice([16, 24, 60])
+    extra = rng.choice([(), (5, 9)])
+    loops = []
+    for cls in (PythonLoop, ChainLoop):
+        cache, sched = make_scheduler(pages)
+        loops.append(cls(sched, cache, extra_stops=extra))
+    plain_loop, chain_loop = loops
+    arrivals = sorted((rng.choice([0, 0, 0, 6, 20, 21, 50]), [rng.randrange(VOCAB) for _ in range(rng.randint(1, 30))],
+                       random_params(random.Random(seed * 77 + i))) for i in range(10))
+    cancel_at = {rng.randint(3, 40): rng.randint(1, 10)}
+    ids = {}
+    for loop in loops:
+        now, step, idle = 0, 0, 0
+        while step < 400:
+            for i, (at, prompt, params) in enumerate(arrivals):
+                if at == step:
+                    ids.setdefault(i, []).append(loop.add_request(prompt, params, now))
+            if step in cancel_at:
+                loop.cancel(cancel_at[step])
+            events = loop.step(now)
+            loop.cache.check_invariants()
+            idle = idle + 1 if events is None else 0
+            now += 1000
+            step += 1
+            if idle > 3 and step > 55:
+                break
+    assert not plain_loop.active and not chain_loop.core.has_unfinished()
+    cancelled = set(cancel_at.values())
+    for i, (a, b) in ids.items():
+        assert a == b
+        rec = chain_loop.core.record(b)
+        if a in cancelled:             # a cancelled request ends at a moment that depends on the step count
+            assert rec.finished and plain_loop.outputs[a]["finished"]
+            continue
+        assert rec.tokens == plain_loop.outputs[a]["tokens"], f"request {a}"
+        assert rec.reason.name == plain_loop.outputs[a]["reason"]
+    assert chain_loop.cache.stats(0)["live"] == 0
+    assert chain_loop.core.chained_steps == chain_loop.launches.count("ahead")
+    test_steps_launched_ahead_change_no_token.chained = getattr(test_steps_launched_ahead_change_no_token, "chained", 0) + chain_loop.core.chained_steps
+
+
+def test_chains_do_happen_and_end_where_they_must():
+    cache, sched = make_scheduler(pages=60, max_batch_seqs=4)
+    loop = ChainLoop(sched, cache)
+    greedy = rt.SamplingParams(0.0, 1.0, None, 9, 0, [], None, True)
+    a = loop.add_request([1, 2, 3, 4, 5], greedy, 0)
+    b = loop.add_request([7, 8], rt.SamplingParams(0.8, 1.0, None, 6, 0, [], 11, True), 0)
+    now = 0
+    while loop.core.has_unfinished():
+        loop.step(now)
+        cache.check_invariants()
+        now += 1000
+    # step 0 is the prefill of both; the decodes chain until b nears its limit, then a alone chains until its own
+    assert loop.launches[0] == "now" and loop.launches.count("ahead") >= 5
+    assert len(loop.core.record(a).tokens) == 9 and len(loop.core.record(b).tokens) == 6
+    assert loop.core.dropped_chains == 0
+    # a request that needs a ranking on the host, or one that waits for admission, keeps the steps unchained
+    cache, sched = make_scheduler(pages=60, max_batch_seqs=4)
+    loop = ChainLoop(sched, cache)
+    loop.add_request([1, 2, 3], rt.SamplingParams(1.0, 0.9, None, 6, 0, [], None, True), 0)
+    now = 0
+    while loop.core.has_unfinished():
+        loop.step(now)
+        now += 1000
+    assert loop.launches.count("ahead") == 0
+    # a stop token ends a chained request: its row in the step launched ahead is passed over
+    cache, sched = make_scheduler(pages=60, max_batch_seqs=4)
+    loop = ChainLoop(sched, cache)
+    prompt = [9, 9, 9]
+    free_run, ctx = [], list(prompt)
+    for _ in range(8):
+        free_run.append(int(np.argmax(pseudo_logits(ctx))))
+        ctx.append(free_run[-1])
+    stop_at = free_run[4]
+    first = free_run.index(stop_at)
+    rid = loop.add_request(prompt, rt.SamplingParams(0.0, 1.0, None, 20, 0, [stop_at], None, True), 0)
+    other = loop.add_request([4, 4], rt.SamplingParams(0.0, 1.0, None, 12, 0, [], None, True), 0)
+    now = 0
+    while loop.core.has_unfinished():
+        loop.step(now)
+        cache.check_invariants()
+        now += 1000
+    assert loop.core.record(rid).tokens == free_run[:first] and loop.core.record(rid).reason == rt.FinishReason.Stop
+    assert len(loop.core.record(other).tokens) == 12 and loop.launches.count("ahead") >= 3
