@@ -33,6 +33,7 @@ constexpr int kTileKeys = 16;     // keys one warp works on at a time
 constexpr int kGroupKeys = 64;    // keys the four warps of a CTA cover per pipeline stage
 constexpr int kStages = 2;        // three stages (two CTAs per SM) measured 1 % slower at batch 8, 1 % faster at batch 1
 constexpr int kTicketInts = 65536;   // ticket counters at the start of the scratch, one per (token, key head)
+constexpr int kCodeBeyondBound = 32; // status code: a token's position is not below the launch's max_context
 
 // TMA: the 16-key tiles (16 keys of one head never straddle a page when the page size is a multiple of 16) come as
 // boxes of 16 rows x 64 columns, issued by lane 0 of the warp that owns the tile and awaited on an mbarrier of that
@@ -72,6 +73,19 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         return;
     }
     const int pos = positions[t];
+    if (pos >= num_splits * split_keys) {
+        // The token lies beyond the context bound that this launch was sized for (the caller's max_context): the
+        // splits that would hold its newest keys do not exist, and the merge below would wait for tickets that
+        // nobody draws. Treated like a padded row: zeros, no ticket (the counters stay zero for the next launch),
+        // and a code for the caller where it gave a status word.
+        if (split == 0) {
+            pdl_wait();
+            for (int i = threadIdx.x; i < group * HD; i += blockDim.x)
+                out[(static_cast<size_t>(t) * nq + kvh * group) * HD + i] = __float2bfloat16_rn(0.f);
+            if (status != nullptr && threadIdx.x == 0) atomicCAS(status, 0, kCodeBeyondBound);
+        }
+        return;
+    }
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     const int lo = split * split_keys;
     if (lo > pos || lo + split_keys <= first) return;   // uniform for the CTA
@@ -434,12 +448,15 @@ int launch_decode(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, cons
         map_v = tc::cached_map(v_pages, cache_rows, HD, HD, kTileKeys);
     }
     const bool tma = map_k != nullptr && map_v != nullptr;
-    static bool configured = false;
-    if (!configured) {
+    // the shared-memory limit is an attribute of the kernel on one device: raised once on every device that launches
+    static bool configured[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return STRIDE_BAD_ARGUMENT;
+    if (!configured[device]) {
         cudaError_t e = cudaFuncSetAttribute(paged_decode_split_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_decode_split_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
+        configured[device] = true;
     }
     static const CUtensorMap no_map = {};
     const dim3 grid(num_splits, nkv, tokens);
@@ -470,9 +487,11 @@ long long stride_paged_decode_scratch_floats(int tokens, int nq, int nkv, int hd
 
 // One query token per entry of the flat batch (decode). `scratch` must be zero when it is
 // first used (the ticket counters at its start; every launch leaves them zero again) and
-// belongs to one stream at a time. Returns -2 for sizes it does not run (head sizes other
-// than 64 and 128, groups above 16, more than 65535 tokens, more than 65536 (token, key head)
-// pairs); the caller then uses the generic kernel.
+// belongs to one stream at a time. `max_context` must exceed every token's position: a row
+// whose position does not lie below it gets zeros (and code 32 in the status word, where one
+// is given), and the scratch stays usable. Returns -2 for sizes it does not run (head sizes
+// other than 64 and 128, groups above 16, more than 65535 tokens, more than 65536 (token,
+// key head) pairs); the caller then uses the generic kernel.
 int stride_paged_decode_attention_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                       int num_pages, const int32_t* block_table, int table_width, const int32_t* seq_of_token,
                                       const int32_t* positions, float* scratch, long long scratch_floats, int tokens, int nq,

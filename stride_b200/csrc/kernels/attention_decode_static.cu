@@ -1,7 +1,9 @@
 // The allocation-free variant of decode attention declared in
-// attention_decode_static.h: same kernels as attention_decode.cu, with the
-// partial results of the key splits kept in an array that is part of this
-// library's device image instead of a buffer the caller allocates.
+// attention_decode_static.h: the kernel of attention_decode.cu in its cp.async
+// form (the TMA form needs a status word and the cache's extent, which this
+// entry point does not take), with the partial results of the key splits kept
+// in an array that is part of this library's device image instead of a buffer
+// the caller allocates.
 #include "attention_decode_static.h"
 
 #include "attention_decode.cu"   // the kernels and their launcher; nothing there is changed

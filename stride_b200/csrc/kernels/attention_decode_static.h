@@ -30,6 +30,14 @@
 //     calls that overlap on the GPU (different streams, or one device driven
 //     from two threads) overwrite each other's partial results and tickets:
 //     run them one after the other.
+//   * max_context must exceed every token's position. A row whose position does
+//     not lie below it gets zeros instead of attention and draws no ticket, so
+//     the array stays clean for the next call (there is no way to reset it
+//     short of unloading the library, so nothing may leave a ticket behind).
+//   * The key and value tiles are copied with cp.async. The ordinary entry
+//     point can also copy them by TMA, for which it needs the size of the cache
+//     and a status word that this signature does not have; the arithmetic and
+//     the order of every sum are the same, so both give the same bits.
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
 //
 // Inputs and outputs are the caller's, with the meanings of

@@ -114,16 +114,17 @@ def first_divergence(candidate: list, reference: list, cosine_floor: float = 0.9
 
 
 def report(name: str, agreement: Agreement, dtype) -> str:
-    ok, why = agreement.verdict(dtype)
+    """One line for the verdict and one for the measures it rests on, e.g.
+
+        chunk=16 [same] cosine 0.999999999 over 1 row | largest difference 1.2e-07 | first token agrees 100.0%, top-5 shared 100.0%
+          differing rows: widest reference margin 0.0000, decisive 0.0% | equivalent: ...
+    """
+    same, why = agreement.verdict(dtype)
     a = agreement
-    return "\n".join([
-        f"{name}: {'EQUIVALENT' if ok else 'DIVERGENT'}",
-        f"  positions compared      {a.positions}",
-        f"  cosine similarity       {a.cosine:.9f}",
-        f"  max absolute difference {a.max_abs_diff:.3e}",
-        f"  argmax agreement        {a.argmax_match_rate:.2%}",
-        f"  top-5 overlap           {a.top5_overlap:.2%}",
-        f"  worst disagreement gap  {a.worst_disagreement_gap:.4f}",
-        f"  decisive disagreements  {a.decisive_disagreement_rate:.2%}",
-        f"  {why}",
-    ])
+    rows = "row" if a.positions == 1 else "rows"
+    head = (f"{name} [{'same' if same else 'DIFFERENT'}] cosine {a.cosine:.9f} over {a.positions} {rows} | "
+            f"largest difference {a.max_abs_diff:.1e} | first token agrees {a.argmax_match_rate:.1%}, "
+            f"top-5 shared {a.top5_overlap:.1%}")
+    tail = (f"  differing rows: widest reference margin {a.worst_disagreement_gap:.4f}, "
+            f"decisive {a.decisive_disagreement_rate:.1%} | {why}")
+    return head + "\n" + tail

@@ -61,6 +61,10 @@ class ModelRunner:
         self.device = self.rt.device
         self.groups = cache_manager.num_groups
         self.token_capacity, self.seq_capacity, self.row_capacity = token_capacity, seq_capacity, row_capacity
+        if max_model_len > model.spec.max_positions:
+            raise ValueError(f"max_model_len {max_model_len} exceeds the {model.spec.max_positions} positions the model's "
+                             "position tables hold")
+        self.max_model_len = int(max_model_len)
         self.table_width = max(1, cache_manager.pages_for(max_model_len))
         self._rt_mod = load_runtime()
         self._eager = _Staging(self._rt_mod.packed_layout(self.groups, token_capacity, seq_capacity, row_capacity,
@@ -88,8 +92,11 @@ class ModelRunner:
         if batch.num_tokens > self.token_capacity or batch.num_seqs > self.seq_capacity:
             raise ValueError(f"the step has {batch.num_tokens} tokens of {batch.num_seqs} requests; the runner was sized "
                              f"for {self.token_capacity} and {self.seq_capacity}")
-        if batch.max_pages > self.table_width:
-            raise ValueError("a request is longer than max_model_len")
+        # Checked here, on the host, for every caller (scheduler, trace replay, the raw step function): the block
+        # table is as wide as max_model_len rounded up to a page, but the position tables end at max_model_len, and
+        # no kernel checks a position against them (python/stride_worker/cache.py:82-86 raises before it touches memory).
+        if batch.max_ctx > self.max_model_len or batch.max_pages > self.table_width:
+            raise ValueError(f"a request would reach position {batch.max_ctx - 1}; max_model_len is {self.max_model_len}")
         if self.cuda_graphs and batch.decode_only and batch.num_rows == batch.num_seqs:
             logits = self._step_graph(batch)
             return logits.cpu() if to_host else logits

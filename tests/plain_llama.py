@@ -3,8 +3,10 @@
 This file is the yardstick of the test-suite. It is written from the formulas
 of the reference project (each function cites the file and lines it restates)
 and shares no code with the ``stride_b200`` package: it never imports it.
-Everything runs on the CPU in the dtype that the caller names (float32 by
-default, float64 for a reference that rounding cannot blur).
+Everything runs where the weights live (the CPU in most tests; a CUDA device
+for the models that are too wide for it) in the dtype that the caller names
+(float32 by default, float64 for a reference that rounding cannot blur). The
+rotation tables are always computed on the CPU in float32 and then moved.
 
 Weights are a plain ``dict`` from checkpoint tensor names to tensors, with the
 names of ``python/stride_worker/model.py:120-171``.
@@ -92,8 +94,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
         raise ValueError(f"{nq} query heads do not group into {nkv} KV heads")
     group = nq // nkv
     out = torch.empty_like(q)
-    i = torch.arange(n).unsqueeze(1)
-    j = torch.arange(n).unsqueeze(0)
+    i = torch.arange(n, device=q.device).unsqueeze(1)
+    j = torch.arange(n, device=q.device).unsqueeze(0)
     allowed = j <= i
     if window is not None:
         allowed &= j > i - window
@@ -158,11 +160,13 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float32, hidden_states
     (python/stride_worker/model.py:120-130, 250-341).
     """
     w = {k: t.to(dtype) for k, t in weights.items()}
-    ids = torch.as_tensor(tokens, dtype=torch.long)
+    device = w["model.embed_tokens.weight"].device
+    ids = torch.as_tensor(tokens, dtype=torch.long).to(device)
     nq = int(cfg["num_attention_heads"])
     hd = int(cfg.get("head_dim", int(cfg["hidden_size"]) // nq))
     cos, sin = rope_tables(hd, torch.arange(len(ids)), float(cfg.get("rope_theta", 10000.0)),
                            cfg.get("rope_scaling"))
+    cos, sin = cos.to(device), sin.to(device)
     x = w["model.embed_tokens.weight"][ids]
     for i in range(int(cfg["num_hidden_layers"])):
         x = decoder_layer(x, w, i, cfg, cos, sin)

@@ -71,7 +71,7 @@ def test_non_finite_logits_and_shape_mismatches_are_refused():
     with pytest.raises(ValueError, match="shapes differ"):
         compare_logits(a[:, :10], a)
     one = compare_logits(a[0], a[0])                      # a single row is a [1, vocab] comparison
-    assert one.positions == 1 and "EQUIVALENT" in report("row", one, torch.float32)
+    assert one.positions == 1 and "[same]" in report("row", one, torch.float32)
     assert isinstance(one, Agreement)
 
 

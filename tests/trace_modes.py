@@ -71,6 +71,38 @@ def mixed(requests: dict, live_limit: int = 4, seed: int = 0, decode_tail: int =
     return steps
 
 
+def decoding_together(requests: dict, decode_steps: int = 8, prompts_per_step: int = 4) -> list[dict]:
+    """Every request live at once: the prompts (all but the last ``decode_steps`` tokens of each) go in a few at a
+    time, then all requests bring one token a step for ``decode_steps`` steps, so that the decode-only steps have as
+    many rows as there are requests."""
+    steps, ids = [], list(requests)
+    for at in range(0, len(ids), prompts_per_step):
+        entries = []
+        for rid in ids[at:at + prompts_per_step]:
+            head = max(1, len(requests[rid]) - decode_steps)
+            entries.append({"id": rid, "tokens": list(requests[rid][:head]), "want": [head - 1]})
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    for k in range(decode_steps, 0, -1):
+        entries = [{"id": rid, "tokens": [t[len(t) - k]], "want": [0]} for rid, t in requests.items() if len(t) - k >= 1]
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    steps[-1]["end"] = ids
+    return steps
+
+
+def restrict_wants(steps: list[dict], keep: dict) -> list[dict]:
+    """The same steps with logits wanted only at the positions ``keep[request]`` (a set): wide vocabularies make
+    every row expensive to hold and to compare."""
+    held: dict = {}
+    for s in steps:
+        for e in s["entries"]:
+            base = held.get(e["id"], 0)
+            e["want"] = [w for w in e["want"] if base + w in keep[e["id"]]]
+            held[e["id"]] = base + len(e["tokens"])
+        for rid in s["end"]:
+            held.pop(rid, None)
+    return steps
+
+
 def expected_rows(steps: list[dict]) -> dict:
     """step number -> list of (request, position) in the order of the logits rows."""
     held: dict = {}
