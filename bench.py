@@ -62,10 +62,23 @@ class ClockSampler:
     def __init__(self):
         self.proc = None
 
+    @staticmethod
+    def _device_id() -> str:
+        """What ``nvidia-smi -i`` should be given for the GPU this process computes on: its UUID, since on a
+        machine with several GPUs the process may have been handed any of them (index 0 of torch is then not
+        index 0 of nvidia-smi)."""
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:  # noqa: BLE001
+            first = os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0].strip()
+            return first or "0"
+
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", "0",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i",
+                                          self._device_id(), "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
         return self

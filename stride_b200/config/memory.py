@@ -59,30 +59,30 @@ class MemoryPlan:
 
 
 def plan_memory(config, dtype: str = "bfloat16", memory_bytes: int = B200_MEMORY_BYTES, block_size: int = 16,
-                activation_fraction: float = 0.15, name: str | None = None) -> MemoryPlan:
-    """``config``: a typed configuration with ``total_params()`` and ``kv_bytes_per_token(itemsize)``.
-    ``activation_fraction`` of what the weights leave is held back for activations, workspace and fragmentation
-    (the worker's ``--activation-reserve``, python/stride_worker/worker.py:182-225). Raises ``PlanError`` when the
-    weights do not fit or not even one page is left."""
+                activation_fraction: float = 0.15, name: str | None = None, max_requests: int = 256) -> MemoryPlan:
+    """``config``: the typed configuration of any registered architecture. Its sizes are taken from the model's
+    own parts (the tensors they declare, what their mixers keep per token and per request), not from arithmetic
+    on the configuration class. ``activation_fraction`` of what the weights leave is held back for activations,
+    workspace and fragmentation (the worker's ``--activation-reserve``, python/stride_worker/worker.py:182-225);
+    state of fixed size is set aside for ``max_requests`` requests. Raises ``PlanError`` when the weights do not
+    fit or not even one page is left."""
     if dtype not in ITEMSIZE:
         raise PlanError(f"dtype must be one of {sorted(ITEMSIZE)}, got {dtype!r}")
     if block_size <= 0:
         raise PlanError("block_size must be positive")
     if not 0.0 <= activation_fraction < 1.0:
         raise PlanError("activation_fraction must be in [0, 1)")
-    item = ITEMSIZE[dtype]
+    from ..engine.loading import footprint      # the parts live above this package; asked for only when a plan is made
+    sizes = footprint(config, dtype)
     name = name or getattr(config, "name", "model")
-    # matrices in the compute dtype, norm weights in float32 (as the loader keeps them)
-    matrices = config.total_params(with_norms=False)
-    vectors = config.total_params(with_norms=True) - matrices
-    weight_bytes = matrices * item + vectors * 4
+    weight_bytes = sizes["weight_bytes"] + sizes["state_bytes_per_request"] * max_requests
     if weight_bytes >= memory_bytes:
         raise PlanError(f"{name}: the weights need {weight_bytes / GIB:.1f} GiB in {dtype} but the device has "
                         f"{memory_bytes / GIB:.1f} GiB")
     after_weights = memory_bytes - weight_bytes
     reserve = int(after_weights * activation_fraction)
     kv_bytes = after_weights - reserve
-    per_token = max(1, config.kv_bytes_per_token(item))
+    per_token = max(1, sizes["kv_bytes_per_token"])
     num_blocks = kv_bytes // (per_token * block_size)
     if num_blocks == 0:
         raise PlanError(f"{name}: {kv_bytes / GIB:.2f} GiB are left for the cache after weights and activations, less than "

@@ -100,6 +100,28 @@ class ScheduleEntry:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become the first residual stream. kind ``lookup``: row ``id`` of the table ``name``
+    [vocab, hidden], no scaling (python/stride_worker/model.py:250-252)."""
+    kind: str
+    vocab: int
+    hidden: int
+    name: str                   # checkpoint name of the table
+    params: tuple = ()          # free-form (key, value) pairs for other kinds (a multiplier, say)
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """How the normed last hidden states become logits. kind ``linear``: ``x @ W.T`` in the compute dtype with a
+    float32 result; ``name`` None ties W to the embedding table (python/stride_worker/model.py:127-130,322-341)."""
+    kind: str
+    vocab: int
+    hidden: int
+    name: Optional[str]
+    params: tuple = ()          # free-form (key, value) pairs for other kinds (a bias, a cap on the logits)
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     hidden: int
@@ -114,6 +136,16 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
     ignorable_tensors: tuple = ()   # glob patterns of checkpoint tensors that may be present and are not read
     extra: Any = field(default=None, compare=False)
+    # The two ends of the model are parts like the rest. Left out, they are the plain kinds built from the two
+    # names above: a table lookup and a linear head.
+    embedding: Optional[EmbeddingSpec] = None
+    head: Optional[HeadSpec] = None
+
+    def embedding_spec(self) -> EmbeddingSpec:
+        return self.embedding or EmbeddingSpec("lookup", self.vocab, self.hidden, self.embed_name)
+
+    def head_spec(self) -> HeadSpec:
+        return self.head or HeadSpec("linear", self.vocab, self.hidden, self.head_name)
 
     @property
     def num_cache_slots(self) -> int:

@@ -121,7 +121,8 @@ def _run(cmd: list[str], what: str) -> None:
 def _build(target: str, sources: list[str], deps: list[str], make_cmd) -> str:
     """Returns the path of an up-to-date shared object for ``target``."""
     out_dir = build_dir()
-    tag = _digest(sources + deps, make_cmd("OUT"))
+    # the tag must not depend on where the tree lies, or a library built in one checkout is built again in a copy of it
+    tag = _digest(sources + deps, [a.replace(HERE, "<csrc>") for a in make_cmd("OUT")])
     out = os.path.join(out_dir, f"{target}.{tag}.so")
     if os.path.exists(out):
         return out
@@ -170,6 +171,20 @@ def build_kernel_library(name: str) -> str:
     return _build(f"kernels_{name}", [src], deps, cmd)
 
 
+def build_external_library(source: str) -> str:
+    """A CUDA source from outside the package (a test's own kernel) compiled with the package's flags and
+    its kernel headers on the include path."""
+    source = os.path.abspath(source)
+    if not os.path.exists(source):
+        raise BuildError(f"no kernel source {source}")
+
+    def cmd(out):
+        return [find_nvcc(), *NVCC_ARCH, *NVCC_FLAGS, "-I", KERNEL_DIR, "-o", out, source, "-lcuda"]
+
+    name = os.path.splitext(os.path.basename(source))[0]
+    return _build(f"external_{name}", [source], _headers(KERNEL_DIR), cmd)
+
+
 def build_runtime() -> str:
     import pybind11
 
@@ -206,6 +221,10 @@ def load_kernel_library(name: str) -> ctypes.CDLL:
         lib = ctypes.CDLL(build_kernel_library(name))
         _kernel_libs[name] = lib
     return lib
+
+
+def load_external_library(source: str) -> ctypes.CDLL:
+    return ctypes.CDLL(build_external_library(source))
 
 
 def build_all(verbose: bool = True) -> list[str]:

@@ -390,6 +390,26 @@ __global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ xt, const fl
         out[static_cast<size_t>(t) * width + c] = __float2bfloat16_rn(__bfloat162float(xt[static_cast<size_t>(t) * width + c]) * factor);
 }
 
+// --------------------------------------------------------------------------- state slots
+// A request's state slot starts at zero: a sequence whose first token of this step sits at position 0 is at its
+// beginning (a new request, or one that is recomputed after it was preempted), so the row of its slot is cleared
+// before any layer runs. Reads only the step's index arrays, so it can sit in a captured graph. One row of CTAs
+// per sequence of the layout (padded ones have q_len 0), 4-byte words.
+__global__ void zero_fresh_state_kernel(uint32_t* __restrict__ state, long long row_words, const int32_t* __restrict__ state_slot,
+                                        const int32_t* __restrict__ q_start, const int32_t* __restrict__ q_len,
+                                        const int32_t* __restrict__ positions, int num_slots) {
+    pdl_trigger();
+    const int s = blockIdx.y;
+    if (q_len[s] <= 0 || positions[q_start[s]] != 0) return;
+    const int slot = state_slot[s];
+    if (slot < 0 || slot >= num_slots) return;
+    pdl_wait();
+    uint32_t* row = state + static_cast<size_t>(slot) * row_words;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < row_words;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        row[i] = 0u;
+}
+
 }  // namespace stride
 
 using namespace stride;
@@ -459,6 +479,20 @@ int stride_add_rmsnorm(float* residual, const void* delta, const float* weight, 
     } else {
         return STRIDE_BAD_ARGUMENT;
     }
+    return STRIDE_LAUNCH_STATUS();
+}
+
+// Clears the state rows [num_slots, row_bytes] of the sequences that start at position 0 in this step.
+// `seq_cap`: entries of state_slot / q_start / q_len (the layout's capacity; padded sequences have q_len 0).
+int stride_zero_fresh_state(void* state, long long row_bytes, int num_slots, const int32_t* state_slot, const int32_t* q_start,
+                            const int32_t* q_len, const int32_t* positions, int seq_cap, cudaStream_t stream) {
+    if (row_bytes <= 0 || row_bytes % 4 || num_slots <= 0 || seq_cap < 0 || seq_cap > 65535) return STRIDE_BAD_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(state) % 4) return STRIDE_BAD_ARGUMENT;
+    if (seq_cap == 0) return 0;
+    const long long words = row_bytes / 4;
+    const unsigned blocks = static_cast<unsigned>(words >= 65536 ? 64 : (words + 255) / 256 > 0 ? (words + 255) / 256 : 1);
+    stride::launch(zero_fresh_state_kernel, dim3(blocks, seq_cap), dim3(256), 0, stream, static_cast<uint32_t*>(state), words, state_slot,
+                   q_start, q_len, positions, num_slots);
     return STRIDE_LAUNCH_STATUS();
 }
 

@@ -179,6 +179,9 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, long long row_st
         }
         s_idx[0] = who;
         s_idx[1] = __float_as_int(remaining_in_segment - run);
+        // every chunk's sum underflowed to zero (a target of zero among denormal weights): no thread below would
+        // write the row, which would then keep the token of an earlier step; the first maximum stands in
+        if (who < 0) out[r] = top.i;
     }
     __syncthreads();
     if (tid == s_idx[0]) {

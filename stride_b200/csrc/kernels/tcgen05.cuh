@@ -29,8 +29,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // Returns false (and records `code`) when the phase did not complete in time. The loop does nothing but
 // try_wait (which itself suspends the thread for a while); every 64th turn it looks at the clock, and gives
 // up when the limit has passed or, once it has waited 50 us, when another wait has already recorded a
-// time-out (so that a kernel that has gone wrong drains quickly).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// time-out (so that a kernel that has gone wrong drains quickly). `limit`: clock cycles; the default is what the
+// kernels of the package use, a test passes a short one to see a wait run out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code, long long limit = kWaitCycles) {
     long long start = 0;
     for (uint32_t turn = 1;; ++turn) {
         uint32_t done;
@@ -46,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
             const long long now = clock64();
             if (start == 0) start = now;
             const long long waited = now - start;
-            if (waited > kWaitCycles) {
+            if (waited > limit) {
                 atomicCAS(status, 0, code);
                 return false;
             }

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "stride_embed_gather": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_add_rmsnorm": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "stride_add_residual": ("elementwise", [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
+    "stride_zero_fresh_state": ("elementwise", [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "stride_rope_kv_write": ("elementwise", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "stride_silu_mul": ("elementwise", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
@@ -154,6 +155,17 @@ def add_residual(residual, delta) -> None:
                                       _code(delta.dtype), _stream()), "add_residual")
 
 
+def zero_fresh_state(state, state_slot, q_start, q_len, positions) -> None:
+    """Clears ``state[slot]`` for every sequence of the step whose first token sits at position 0 (``state``:
+    [num_slots, ...] of a 4-byte element type; the index arrays are the step's, at their layout's capacity)."""
+    if state.element_size() != 4:
+        raise KernelError("state rows must have a 4-byte element type")
+    row_bytes = (state.numel() // state.shape[0]) * 4
+    _check(_fn("stride_zero_fresh_state")(_dev(state, "state"), row_bytes, state.shape[0], _dev(state_slot, "state_slot", torch.int32),
+                                          _dev(q_start, "q_start", torch.int32), _dev(q_len, "q_len", torch.int32),
+                                          _dev(positions, "positions", torch.int32), q_len.shape[0], _stream()), "zero_fresh_state")
+
+
 def rope_kv_write(qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages, nq: int, nkv: int, hd: int,
                   page_size: int, rotate: bool = True) -> None:
     tokens = qkv.shape[0]
@@ -198,7 +210,16 @@ _TC_TICKETS = 8192
 _tc_state: dict = {}
 
 
+def _device_key(device) -> torch.device:
+    """``cuda`` and ``cuda:<current>`` are one device: state kept per device must not be kept twice."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device() if torch.cuda.is_available() else 0)
+    return device
+
+
 def _tc_buffers(device, partial_floats: int):
+    device = _device_key(device)
     st = _tc_state.get(device)
     if st is None:
         st = {"tickets": torch.zeros(_TC_TICKETS, dtype=torch.int32, device=device),
@@ -224,29 +245,50 @@ def _tc_scratch_floats(n_out: int, tokens: int, k: int) -> int:
 def tc_status(device=None) -> int:
     """0, or the code of the first bounded wait that ran out inside the tcgen05
     kernels (1 producer, 2 tensor-core issuer, 3 epilogue). Synchronises."""
-    codes = [int(st["status"][0].item()) for dev, st in _tc_state.items() if device is None or dev == device]
+    codes = [int(st["status"][0].item()) for dev, st in _tc_state.items() if device is None or dev == _device_key(device)]
     return next((c for c in codes if c), 0)
 
 
-_WAIT_CODES = {1: "matrix product: producer", 2: "matrix product: tensor-core issuer", 3: "matrix product: epilogue"}
+_WAIT_CODES = {1: "matrix product: producer", 2: "matrix product: tensor-core issuer", 3: "matrix product: epilogue",
+               31: "decode attention: a tile copy", 41: "weight-streaming product: a tile copy"}
+_WAIT_CODES.update({c: "prefill attention (attention_prefill_tc.cu)" for c in range(11, 22)})
+_OTHER_CODES = {32: "decode attention was given a token whose position is not below the context bound of its launch"}
 
 
-def raise_on_kernel_status(code: int) -> None:
-    """Raises when ``code`` (the status word, read back by the caller) is not 0: a bounded wait inside a
-    tcgen05 kernel ran out, so what that kernel wrote is not to be trusted."""
-    if code:
-        raise KernelError(f"a bounded wait inside a tcgen05 kernel ran out (code {code}: "
-                          f"{_WAIT_CODES.get(code, 'attention, see attention_prefill_tc.cu')}); the step's results are invalid")
+def reset_kernel_status(device=None) -> None:
+    """Sets the status word back to 0 (on ``device``, or wherever one exists), so that later steps are judged on
+    their own: the kernels only ever write the first code into a word that is still 0."""
+    for dev, st in _tc_state.items():
+        if device is None or dev == _device_key(device):
+            st["status"].zero_()
+
+
+def raise_on_kernel_status(code: int, device=None) -> None:
+    """Raises when ``code`` (the status word, read back by the caller) is not 0: a bounded wait inside a kernel ran
+    out, or a kernel refused a row, so what the step wrote is not to be trusted. With ``device`` the word there is
+    cleared first, so that the failure is reported once and the next step starts clean (the reference's worker
+    reports a failed pass and keeps serving, python/stride_worker/worker.py:156-165)."""
+    if not code:
+        return
+    if device is not None:
+        reset_kernel_status(device)
+    if code in _OTHER_CODES:
+        raise KernelError(f"kernel status {code}: {_OTHER_CODES[code]}; the step's results are invalid")
+    raise KernelError(f"a bounded wait inside a kernel ran out (code {code}: {_WAIT_CODES.get(code, 'unknown place')}); "
+                      "the step's results are invalid")
 
 
 def check_kernel_status(device=None) -> None:
-    """Reads the status word (synchronises) and raises if a kernel recorded a timed-out wait."""
-    raise_on_kernel_status(tc_status(device))
+    """Reads the status word (synchronises), clears it if it is set, and raises if a kernel recorded a failure."""
+    code = tc_status(device)
+    if code:
+        reset_kernel_status(device)
+    raise_on_kernel_status(code)
 
 
 def status_tensor(device):
     """The device word that the tcgen05 kernels set on a timed-out wait (for callers that copy it with their own results)."""
-    return _tc_buffers(torch.device(device), 0)["status"]
+    return _tc_buffers(device, 0)["status"]
 
 
 def linear_tc(x, weight, out) -> bool:

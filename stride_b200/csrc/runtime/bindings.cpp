@@ -313,7 +313,7 @@ PYBIND11_MODULE(_runtime, m) {
         .def("adopt_chain", &Scheduler::adopt_chain)
         .def("on_tokens", &Scheduler::on_tokens, py::arg("outputs"), py::arg("now"))
         .def("stop", &Scheduler::stop)
-        .def("cancel", &Scheduler::cancel)
+        .def("cancel", &Scheduler::cancel, py::arg("request"), py::arg("publish") = true)
         .def("forget", &Scheduler::forget)
         .def("sequence", &Scheduler::sequence, py::return_value_policy::copy)
         .def("metrics", [](const Scheduler& s) {
@@ -356,7 +356,7 @@ PYBIND11_MODULE(_runtime, m) {
         .def_property_readonly("num_live", &EngineCore::num_live)
         .def("record", &EngineCore::record, py::return_value_policy::copy)
         .def("forget", &EngineCore::forget)
-        .def("cancel", &EngineCore::cancel)
+        .def("cancel", &EngineCore::cancel, py::arg("request"), py::arg("publish") = true)
         .def("begin_step", &EngineCore::begin_step, py::arg("now"))
         .def("batch", [](EngineCore& c) { return &c.batch(); }, py::return_value_policy::reference_internal)
         .def("rows", &EngineCore::rows)

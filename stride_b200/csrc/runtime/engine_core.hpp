@@ -94,9 +94,9 @@ public:
         if (it != records_.end() && it->second.finished) records_.erase(it);
     }
 
-    std::vector<StepEvent> cancel(int64_t request) {
+    std::vector<StepEvent> cancel(int64_t request, bool publish = true) {
         std::vector<StepEvent> events;
-        for (auto& f : sched_->cancel(request)) {
+        for (auto& f : sched_->cancel(request, publish)) {
             events.push_back(StepEvent{f.request, false, 0, FinishReason::Cancelled});
             retire(f.seq, FinishReason::Cancelled, &f);
         }
@@ -241,13 +241,28 @@ public:
         return events;
     }
 
-    // Gives up an open step whose launch failed: nothing was sampled. Fatal for the requests in it, as in the
-    // reference, whose scheduler has already advanced them; the caller is expected to stop.
-    void abandon_step() {
+    // Gives up the open step (and a step chained after it) because the device reported a failure: nothing was
+    // sampled. Returns the requests that had work in those steps. The scheduler has already advanced them, as in
+    // the reference (crates/stride-sched/src/lib.rs:431-440), so they cannot go on; the caller cancels them and
+    // keeps serving the others.
+    std::vector<int64_t> abandon_step() {
+        std::vector<int64_t> requests;
+        auto collect = [&](const StepBatch* b) {
+            if (!b) return;
+            for (auto& item : b->items()) {
+                auto it = live_.find(item.request);
+                if (it != live_.end() && std::find(requests.begin(), requests.end(), it->second.request) == requests.end())
+                    requests.push_back(it->second.request);
+            }
+        };
+        collect(batch_.get());
+        collect(next_batch_.get());
         in_step_ = false;
+        launched_ = false;
         batch_.reset();
         next_batch_.reset();
         next_rows_.clear();
+        return requests;
     }
 
 private:

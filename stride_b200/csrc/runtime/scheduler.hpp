@@ -355,13 +355,15 @@ public:
 
     std::optional<Finished> stop(SeqId id) { return retire(id, FinishReason::Stop); }
 
-    std::vector<Finished> cancel(int64_t request) {
+    // `publish` false: the request's pages go back without being indexed for sharing (what they hold is not to
+    // be trusted, e.g. after a step that the device reported as failed).
+    std::vector<Finished> cancel(int64_t request, bool publish = true) {
         std::vector<SeqId> ids;
         for (auto& kv : seqs_)
             if (kv.second.request == request && kv.second.state != SeqState::Finished) ids.push_back(kv.first);
         std::vector<Finished> out;
         for (SeqId id : ids)
-            if (auto f = retire(id, FinishReason::Cancelled)) out.push_back(std::move(*f));
+            if (auto f = retire(id, FinishReason::Cancelled, publish)) out.push_back(std::move(*f));
         return out;
     }
 
@@ -437,7 +439,7 @@ private:
         return PrefillChunk{id, start, len, s.cached_prefix_len};
     }
 
-    std::optional<Finished> retire(SeqId id, FinishReason reason) {
+    std::optional<Finished> retire(SeqId id, FinishReason reason, bool publish = true) {
         auto it = seqs_.find(id);
         if (it == seqs_.end() || it->second.state == SeqState::Finished) return std::nullopt;
         Sequence& s = it->second;
@@ -446,7 +448,7 @@ private:
         Finished f{id, s.request, reason, std::vector<TokenId>(s.tokens.begin() + s.prompt_len, s.tokens.end()),
                    s.ttft_us(), s.mean_itl_us(), s.cached_prefix_len};
         if (cache_->has(id)) {
-            cache_->publish(id, s.tokens, s.kv_len);
+            if (publish) cache_->publish(id, s.tokens, s.kv_len);
             cache_->close(id);
         }
         running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());

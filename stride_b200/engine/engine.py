@@ -9,6 +9,15 @@ and retire those that reached their limit. Time is a logical clock in
 microseconds advanced by each step's measured duration, or by 1000 when nothing
 could be scheduled (lib.rs:301-306,379).
 
+Every rule of that loop lives in the C++ ``EngineCore`` (``csrc/runtime/
+engine_core.hpp``): scheduling, the sampler's parameters, stop rules, retiring.
+This class is the device half: it launches the step function and the sampling
+kernel between the core's ``begin_step`` and ``finish_step`` and moves the few
+bytes in between. When the open step holds single decoded tokens only, the step
+after it is launched before this one's tokens are read (``chain_step``): its
+token ids are copied on the device from the sampled tokens, so the GPU never
+waits for the host between two decode steps.
+
 Sampling: greedy and plain-temperature rows are drawn by a kernel on the device
 (only token ids come back to the host); rows with top-k or top-p are ranked by
 the host sampler from their logits. Either way the request's own seeded
@@ -52,15 +61,27 @@ class RequestOutput:
     seed: int = 0
 
 
-class _Active:
-    __slots__ = ("request_id", "seq", "sampler", "greedy", "ranked", "temperature", "output")
+class _Launch:
+    """Pinned host buffers of one launched step: the sampler's parameters going in, tokens and the kernels'
+    status word coming out. Two of them take turns, since a step may be launched while the one before it is
+    still being read."""
 
-    def __init__(self, request_id, seq, sampler, output):
-        self.request_id, self.seq, self.sampler, self.output = request_id, seq, sampler, output
-        p = sampler.params
-        self.greedy = p.is_greedy()
-        self.ranked = p.needs_ranking()
-        self.temperature = 0.0 if self.greedy else float(p.temperature)
+    def __init__(self, rows: int, device):
+        pin = torch.device(device).type == "cuda"
+        self.sample_host = torch.zeros(3 * rows, dtype=torch.float32, pin_memory=pin)
+        host = self.sample_host.numpy()
+        self.temperature, self.uniform = host[:rows], host[rows:2 * rows]
+        self.suppress = host[2 * rows:3 * rows].view(np.int32)
+        self.tokens_host = torch.zeros(rows, dtype=torch.int32, pin_memory=pin)
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
+        self.done = torch.cuda.Event()
+        self.rows = 0
+        self.ranked: list = []
+        self.logits = None
+        self.record: dict = {}
+
+
+_REASONS = {"Length": "length", "Stop": "stop", "Cancelled": "cancelled", "Preempted": "preempted"}
 
 
 class Engine:
@@ -97,18 +118,19 @@ class Engine:
                                      self.cfg.watermark, self.cfg.chunked_prefill), self.cache)
         self.eos = eos_token_id if eos_token_id is not None else (spec.eos_token_ids[0] if spec.eos_token_ids else -1)
         self.extra_eos = tuple(spec.eos_token_ids[1:]) if eos_token_id is None else ()
+        self.core = self._rt.EngineCore(self.scheduler, self.eos, list(self.extra_eos), self.cfg.seed & 0xFFFFFFFFFFFFFFFF,
+                                        self.cfg.max_queued, self.model.vocab)
         self.now = 0
-        self._next_request = 1
-        self._active: dict[int, _Active] = {}           # by sequence id
         self._outputs: dict[int, RequestOutput] = {}    # by request id
         self._seq_of_request: dict[int, int] = {}
-        pin = self.model.rt.device.type == "cuda"
-        self._sample_host = torch.zeros(3 * row_cap, dtype=torch.float32, pin_memory=pin)
-        self._sample_dev = torch.zeros(3 * row_cap, dtype=torch.float32, device=self.model.rt.device)
-        self._tokens_dev = torch.zeros(row_cap, dtype=torch.int32, device=self.model.rt.device)
-        self._tokens_host = torch.zeros(row_cap, dtype=torch.int32, pin_memory=pin)
-        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)     # the kernels' timed-out-wait word, read back with the tokens
+        dev = self.model.rt.device
+        self._sample_dev = torch.zeros(3 * row_cap, dtype=torch.float32, device=dev)
+        self._tokens_dev = torch.zeros(row_cap, dtype=torch.int32, device=dev)
+        self._launches = [_Launch(row_cap, dev), _Launch(row_cap, dev)]
+        self._turn = 0
+        self._ahead: Optional[_Launch] = None           # a step launched before the one before it was read
         self._row_cap = row_cap
+        self._mark = None                               # when the device was last known to be busy with a launched step
         self.forward_passes = 0
         self.last_step: dict = {}
         self.busy_us = 0
@@ -119,43 +141,26 @@ class Engine:
     def add_request(self, tokens: Sequence[int], params=None, tenant: str = "default", klass: str = "interactive") -> int:
         """Queues one request; returns its id. Raises ValueError when the
         sampling parameters are invalid, the prompt is empty or too long, or a
-        token lies outside the vocabulary."""
-        if self.scheduler.num_waiting >= self.cfg.max_queued:
-            # the reference's engine tells its API layer to back off at this point (crates/stride-engine/src/lib.rs:68-70)
-            raise EngineBusy(f"{self.scheduler.num_waiting} requests are waiting for admission (max_queued {self.cfg.max_queued})")
+        token lies outside the vocabulary; ``EngineBusy`` when too many requests
+        wait for admission already (the reference's engine tells its API layer to
+        back off at that point, crates/stride-engine/src/lib.rs:68-70)."""
         params = params if params is not None else self._rt.SamplingParams()
-        tokens = [int(t) for t in tokens]
-        for t in tokens:
-            if not 0 <= t < self.model.vocab:
-                raise ValueError(f"token {t} lies outside the vocabulary of {self.model.vocab}")
-        if self.extra_eos:
-            params = self._with_stops(params, self.extra_eos)
         service = {"interactive": self._rt.ServiceClass.Interactive, "batch": self._rt.ServiceClass.Batch,
                    "background": self._rt.ServiceClass.Background}[klass]
-        rid = self._next_request
-        seq = self.scheduler.admit(rid, tenant, tokens, params, service, self.now)
-        self._next_request += 1
-        # fallback seed: base + request id (+ index 0), crates/stride-engine/src/lib.rs:278-287
-        seed = (self.cfg.seed + rid) & 0xFFFFFFFFFFFFFFFF
-        sampler = self._rt.Sampler(params, self.eos, seed)
-        out = RequestOutput(rid, len(tokens), [], seed=sampler.effective_seed)
-        self._active[seq] = _Active(rid, seq, sampler, out)
-        self._outputs[rid] = out
-        self._seq_of_request[rid] = seq
+        try:
+            rid = self.core.add_request([int(t) for t in tokens], params, tenant, service, self.now)
+        except self._rt.EngineBusy as e:
+            raise EngineBusy(str(e)) from None
+        record = self.core.record(rid)
+        self._outputs[rid] = RequestOutput(rid, record.prompt_len, [], seed=record.seed)
+        self._seq_of_request[rid] = record.seq
         return rid
 
-    def _with_stops(self, params, extra):
-        p = self._rt.SamplingParams(params.temperature, params.top_p, params.top_k, params.max_tokens, params.min_tokens,
-                                    list(params.stop_tokens) + [e for e in extra if e not in params.stop_tokens],
-                                    params.seed, params.ignore_eos)
-        return p
-
     def cancel(self, request_id: int) -> None:
-        for f in self.scheduler.cancel(request_id):
-            self._retire(f.seq, "cancelled", f)
+        self._apply(self.core.cancel(request_id))
 
     def has_unfinished(self) -> bool:
-        return bool(self._active)
+        return self.core.has_unfinished()
 
     def output(self, request_id: int) -> RequestOutput:
         return self._outputs[request_id]
@@ -165,105 +170,117 @@ class Engine:
         """One scheduling step. Returns [(request_id, token or None, finish_reason or None)]:
         a token for every request that produced one, and a reason for every
         request that ended in this step."""
-        batch = self.scheduler.step(self.now)
-        if self.cfg.check_invariants:
-            self.cache.check_invariants()
-        if batch.is_empty():
+        core = self.core
+        if not core.begin_step(self.now):
+            self._ahead = None
+            if self.cfg.check_invariants:
+                self.cache.check_invariants()
             self.now += 1000
             return []
+        if self.cfg.check_invariants:
+            self.cache.check_invariants()
         started = time.perf_counter()
-        step_batch = self.scheduler.build_batch(batch)
-        if _NVTX:
-            torch.cuda.nvtx.range_push(f"stride.step tokens={step_batch.num_tokens} seqs={step_batch.num_seqs}")
-        logits = self.runner.step(step_batch)
-        seqs = step_batch.row_requests()
-        tokens = self._sample(logits, seqs)
-        if _NVTX:
-            torch.cuda.nvtx.range_pop()
-        self.scheduler.after_step(batch)
-        duration = int((time.perf_counter() - started) * 1e6)
+        if core.launched_ahead():
+            launch = self._ahead
+            started = self._mark or started
+        else:
+            self._ahead = None                  # a chained step that no request survived to use: its results are never read
+            launch = self._launch(core.batch(), None)
+        self._ahead = None
+        try:
+            if self.cfg.chain_steps and core.chain_step():
+                self._ahead = self._launch(core.next_batch(), launch)
+            tokens, ranked_logits = self._collect(launch)
+        except ops.KernelError:
+            self._fail()
+            raise
+        self._mark = time.perf_counter()
+        duration = int((self._mark - started) * 1e6)
         # the record of the step (python/stride_worker/model.py:238-240,343-345 measures the same span on the worker)
-        self.last_step = {"tokens": step_batch.num_tokens, "seqs": step_batch.num_seqs, "rows": len(seqs),
-                          "decode_only": step_batch.decode_only, "us": duration}
+        self.last_step = dict(launch.record, us=duration)
         self.forward_passes += 1
         self.busy_us += duration
         self.now += max(duration, 1)
-        self.h2d_bytes += self.runner.last_h2d_bytes
-        events, sampled, stopped = [], [], []
-        for seq, token in zip(seqs, tokens):
-            a = self._active.get(seq)
-            if a is None:
-                continue
-            if a.sampler.is_stop(token):
-                stopped.append(seq)
-            else:
-                sampled.append((seq, token))
-                a.output.tokens.append(token)
-                events.append((a.request_id, token, None))
-        finished = self.scheduler.on_tokens(sampled, self.now)
-        for seq in stopped:
-            f = self.scheduler.stop(seq)
-            events.append((self._active[seq].request_id, None, "stop"))
-            self._retire(seq, "stop", f)
-        for f in finished:
-            events.append((self._active[f.seq].request_id, None, "length"))
-            self._retire(f.seq, "length", f)
+        events = self._apply(core.finish_step(tokens, launch.ranked, ranked_logits, self.now))
         if self.cfg.check_invariants:
             self.cache.check_invariants()
         return events
 
-    def _retire(self, seq, reason, finished) -> None:
-        a = self._active.pop(seq, None)
-        if a is None:
-            return
-        a.output.finished = True
-        a.output.finish_reason = reason
-        if finished is not None:
-            a.output.cached_prompt_tokens = finished.cached_prefix_len
-            a.output.ttft_us = finished.ttft_us
-            a.output.mean_itl_us = finished.mean_itl_us
-        self._seq_of_request.pop(a.request_id, None)
-        self.scheduler.forget(seq)
-
-    # ---------------------------------------------------------------- sampling
-    def _sample(self, logits: torch.Tensor, seqs: list) -> list:
-        n = len(seqs)
-        if n == 0:
-            return []
+    def _launch(self, batch, after: Optional[_Launch]) -> _Launch:
+        """Launches the step function and the sampling kernel for ``batch`` and the copies that bring tokens and
+        status back; returns without waiting. ``after``: the launch whose sampled tokens are this step's token
+        ids (a chained step), copied on the device."""
+        launch = self._launches[self._turn]
+        self._turn ^= 1
+        chained = after is not None
+        n = batch.num_rows
+        if _NVTX:
+            torch.cuda.nvtx.range_push(f"stride.step tokens={batch.num_tokens} seqs={batch.num_seqs} chained={chained}")
+        logits = self.runner.step(batch, token_source=self._tokens_dev[:after.rows] if chained else None)
         cap = self._row_cap
-        host = self._sample_host.numpy()
-        temperature, uniform = host[:cap], host[cap:2 * cap]
-        suppress = host[2 * cap:3 * cap].view(np.int32)
-        ranked_rows = []
-        for r, seq in enumerate(seqs):
-            a = self._active[seq]
-            generated = len(a.output.tokens)
-            suppress[r] = a.sampler.suppressed_token(generated)
-            if a.ranked:
-                ranked_rows.append(r)
-                temperature[r] = 0.0
-                uniform[r] = 0.0
-            else:
-                temperature[r] = a.temperature
-                uniform[r] = 0.0 if a.greedy else a.sampler.next_uniform()
-        self._sample_dev.copy_(self._sample_host, non_blocking=True)
-        dev = self._sample_dev
-        ops.sample_rows(logits, self._tokens_dev[:n], temperature=dev[:n], uniform=dev[cap:cap + n],
-                        suppress=dev[2 * cap:2 * cap + n].view(torch.int32))
-        self._tokens_host[:n].copy_(self._tokens_dev[:n], non_blocking=True)
-        self._status_host.copy_(ops.status_tensor(self._tokens_dev.device)[:1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        ops.raise_on_kernel_status(int(self._status_host[0]))
-        self.h2d_bytes += self._sample_host.numel() * 4
+        if chained:
+            self.core.prepare_next_sampling(launch.temperature, launch.uniform, launch.suppress)
+            launch.ranked = []
+        else:
+            launch.ranked = list(self.core.prepare_sampling(launch.temperature, launch.uniform, launch.suppress))
+        launch.rows, launch.logits = n, logits
+        launch.record = {"tokens": batch.num_tokens, "seqs": batch.num_seqs, "rows": n, "decode_only": batch.decode_only,
+                         "chained": chained}
+        if n:
+            dev = self._sample_dev
+            dev.copy_(launch.sample_host, non_blocking=True)
+            ops.sample_rows(logits, self._tokens_dev[:n], temperature=dev[:n], uniform=dev[cap:cap + n],
+                            suppress=dev[2 * cap:2 * cap + n].view(torch.int32))
+            launch.tokens_host[:n].copy_(self._tokens_dev[:n], non_blocking=True)
+            self.h2d_bytes += launch.sample_host.numel() * 4
+        launch.status_host.copy_(ops.status_tensor(self._tokens_dev.device)[:1], non_blocking=True)
+        launch.done.record()
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        self.h2d_bytes += self.runner.last_h2d_bytes
         self.d2h_bytes += n * 4 + 4
-        tokens = self._tokens_host[:n].tolist()
-        if ranked_rows:
-            rows = logits[torch.as_tensor(ranked_rows, device=logits.device)].cpu().numpy()
-            self.d2h_bytes += rows.nbytes
-            for i, r in enumerate(ranked_rows):
-                a = self._active[seqs[r]]
-                tokens[r] = a.sampler.sample(rows[i], len(a.output.tokens))
-        return tokens
+        return launch
+
+    def _collect(self, launch: _Launch):
+        """Waits for one launch (not for what was launched after it) and returns its tokens and, for the rows
+        that the host ranks, their logits."""
+        launch.done.synchronize()
+        ops.raise_on_kernel_status(int(launch.status_host[0]), self._tokens_dev.device)
+        tokens = launch.tokens_host[:launch.rows].numpy().copy()
+        ranked_logits = None
+        if launch.ranked:
+            ranked_logits = launch.logits[torch.as_tensor(launch.ranked, device=launch.logits.device)].cpu().numpy()
+            self.d2h_bytes += ranked_logits.nbytes
+        return tokens, ranked_logits
+
+    def _fail(self) -> None:
+        """A kernel reported a failure: the results of the open step (and of a step chained after it) are not to
+        be trusted. Their requests end with the reason "error" and give their pages back; the engine goes on with
+        the others (python/stride_worker/worker.py:156-165 reports the failed pass and keeps serving)."""
+        torch.cuda.synchronize()
+        ops.reset_kernel_status(self._tokens_dev.device)
+        self._ahead = None
+        for rid in self.core.abandon_step():
+            self._apply(self.core.cancel(rid, publish=False), reason="error")       # what their pages hold is not to be shared
+
+    def _apply(self, core_events, reason: Optional[str] = None) -> list:
+        """Core events into the outputs; returns them as (request, token, reason) tuples."""
+        events = []
+        for e in core_events:
+            out = self._outputs.get(e.request)
+            why = None if e.reason == self._rt.FinishReason.NotFinished else (reason or _REASONS[e.reason.name])
+            if out is not None:
+                if e.token is not None:
+                    out.tokens.append(e.token)
+                if why is not None:
+                    record = self.core.record(e.request)
+                    out.finished, out.finish_reason = True, why
+                    out.cached_prompt_tokens = record.cached_prefix_len
+                    out.ttft_us, out.mean_itl_us = record.ttft_us, record.mean_itl_us
+                    self.core.forget(e.request)
+                    self._seq_of_request.pop(e.request, None)
+            events.append((e.request, e.token, why))
+        return events
 
     # ------------------------------------------------------------ conveniences
     def generate(self, prompts: Sequence[Sequence[int]], params=None, tenant: str = "default",
@@ -285,6 +302,8 @@ class Engine:
     def forward(self, work: Sequence[tuple]) -> torch.Tensor:
         """The raw step function on explicit work: [(request_key, tokens, position, want)].
         The caller manages pages through ``engine.cache`` (open / ensure / close)."""
+        if self._ahead is not None:
+            raise RuntimeError("a step of the engine's own requests is in flight; call step() until they are done")
         batch = self._rt.StepBatch(self.cache)
         for key, tokens, position, want in work:
             batch.add(int(key), [int(t) for t in tokens], int(position), [int(w) for w in want])
@@ -303,5 +322,6 @@ class Engine:
         m.update(forward_passes=self.forward_passes, busy_us=self.busy_us, kv_blocks_total=kv["capacity"],
                  kv_blocks_live=kv["live"], kv_blocks_cached=kv["cached"], kv_block_hit_rate=kv["block_hit_rate"],
                  queued=self.scheduler.num_waiting, running=self.scheduler.num_running,
-                 graph_replays=self.runner.graph_replays, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes)
+                 graph_replays=self.runner.graph_replays, h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes,
+                 chained_steps=self.core.chained_steps, dropped_chains=self.core.dropped_chains)
         return m

@@ -74,6 +74,23 @@ def _declarations(config) -> dict:
     return DecoderModel(config.to_model_spec(), runtime).declare()
 
 
+def footprint(config, dtype: str = "bfloat16") -> dict:
+    """What a model of this configuration needs in bytes, read from its own parts without touching a device: the
+    declared tensors (matrices in the compute dtype, vectors and tables in 32 bits, as the loader keeps them),
+    what its mixers keep per token in pages, and the state of fixed size per request. Works for any registered
+    architecture, since it asks the parts and not the configuration class."""
+    import math
+
+    from ..cache import plan_groups
+    item = torch.empty((), dtype=DTYPES[dtype]).element_size()
+    model = DecoderModel(config.to_model_spec(), Runtime("meta", DTYPES[dtype], 1, 1))
+    weights = sum(math.prod(d.shape) * (item if d.role == "matrix" else 4) for d in model.declare().values() if not d.optional)
+    requests = model.cache_requests()
+    per_token = sum(g.elements_per_token() for g in plan_groups(requests)) * item
+    state = sum(math.prod(s.shape) * torch.empty((), dtype=s.dtype).element_size() for _r, s in requests if s is not None)
+    return {"weight_bytes": int(weights), "kv_bytes_per_token": int(per_token), "state_bytes_per_request": int(state)}
+
+
 @dataclass
 class CachePlan:
     page_size: int

@@ -73,6 +73,7 @@ class ModelRunner:
         self._decode_buckets = _buckets(min(seq_capacity, token_capacity))
         self._graphs: dict[tuple, tuple] = {}        # (batch bucket, context bucket) -> (graph, logits)
         self._stagings: dict[int, _Staging] = {}     # batch bucket -> packed step arrays
+        self._token_source = None
         self.steps = 0
         self.graph_replays = 0
         self.last_h2d_bytes = 0
@@ -80,12 +81,18 @@ class ModelRunner:
         self.replayed_launches = 0      # own kernels run through graph replays
 
     # ------------------------------------------------------------------ public
-    def step(self, batch, to_host: bool = False):
+    def step(self, batch, to_host: bool = False, token_source=None):
         """Runs ``batch`` (a runtime ``StepBatch``). Returns float32 logits
         [batch.num_rows, vocab] in the order of the wanted places: a view of a
         reused device buffer, valid until the next step — or a CPU tensor when
         ``to_host`` is set or the rows exceed the row capacity (they are then
-        produced in slices)."""
+        produced in slices). ``token_source`` (int32 on the device, one per token of
+        the batch): the token ids are taken from there instead of from the batch,
+        by a copy on the device after the step's arrays have been uploaded; this is
+        how a step runs on tokens that the step before it has only just sampled."""
+        self._token_source = token_source
+        if token_source is not None and token_source.shape[0] != batch.num_tokens:
+            raise ValueError("one token id per token of the step is needed")
         self.steps += 1
         if batch.num_tokens == 0:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device="cpu" if to_host else self.device)
@@ -126,6 +133,9 @@ class ModelRunner:
         staging.wait_host_free()
         batch.pack(self.groups, l["token_cap"], l["seq_cap"], l["row_cap"], l["table_width"], staging.host_np)
         staging.upload()
+        source = self._token_source
+        if source is not None:
+            staging.dev[l["token_ids"]: l["token_ids"] + source.shape[0]].copy_(source)
         self.last_h2d_bytes = l["total"] * 4
 
     def _step_eager(self, batch, to_host):
@@ -193,7 +203,7 @@ class ModelRunner:
         if entry is None:
             self._pack(staging, batch)
             ctx = self._context(staging, batch, b, b, for_graph=cb)
-            self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
+            self._warm_up(ctx, batch)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.counters["launches"]
@@ -218,7 +228,7 @@ class ModelRunner:
         if entry is None:
             self._pack(self._eager, batch)
             ctx = self._context(self._eager, batch, batch.num_tokens, batch.num_rows)
-            self.model.forward(ctx)                 # warm-up: allocates every buffer the step touches
+            self._warm_up(ctx, batch)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.counters["launches"]
@@ -233,6 +243,22 @@ class ModelRunner:
         self.graph_replays += 1
         self.replayed_launches += self.launches_per_graph[key]
         return logits[:batch.num_rows]
+
+    def _warm_up(self, ctx, batch) -> None:
+        """One eager run before a capture: it allocates every buffer the step touches and loads what is loaded
+        lazily. The replay that follows runs the same step again. Writing keys and values twice is harmless (the
+        same values to the same places); per-request state is not idempotent, so the rows of the step's requests
+        are put back as they were, and the replay is the one run that counts."""
+        states = self.model._states()
+        if not states:
+            self.model.forward(ctx)
+            return
+        slots = torch.as_tensor([self.cache.state_slot(request) for request, _t, _p, _w in batch.items()], dtype=torch.long,
+                                device=self.device)
+        kept = [state[slots].clone() for state in states]
+        self.model.forward(ctx)
+        for state, rows in zip(states, kept):
+            state[slots] = rows
 
     def captured_buckets(self) -> list[int]:
         return sorted({k[0] for k in self._graphs if k[0] != "portion"})

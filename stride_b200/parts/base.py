@@ -16,6 +16,11 @@ FeedForward   ``forward(x, ctx) -> delta``.
 PositionEncoding  used by a mixer: ``encode_and_store`` rotates queries and keys
               in place and writes keys and values into the pages.
 Layer         ``forward(stream, ctx, cache)``: the arrangement of the above.
+Embedding     ``forward(ctx, out)``: fills the float32 residual rows [tokens, hidden]
+              from ``ctx.token_ids``; ``table()`` is what a tied head may share.
+Head          ``forward(x, out)``: float32 logits [rows, vocab] from the normed rows;
+              ``bind(weights, tied)`` receives the embedding's table when its spec
+              names no tensor of its own.
 
 Adding a kind: subclass the interface, then ``register_part(category, kind, cls)``.
 """
@@ -29,7 +34,7 @@ import torch
 
 from ..weights import TensorDecl
 
-CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer")
+CATEGORIES = ("norm", "mixer", "feed_forward", "position", "layer", "embedding", "head")
 _PARTS: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -53,10 +58,26 @@ def registered_parts(category: str) -> list[str]:
 
 @dataclass(frozen=True)
 class CacheRequest:
-    """Keys and values per token that a mixer keeps in pages."""
-    num_kv_heads: int
-    head_dim: int
-    window: Optional[int] = None     # None: every key is kept
+    """What a mixer keeps per token in pages.
+
+    The plain form is keys and values of one shape: ``CacheRequest(num_kv_heads, head_dim, window)``. A mixer
+    that keeps something else names its tensors: ``CacheRequest(tensors=(("latent", 1, 24),))`` keeps one vector
+    of 24 numbers per token; ``(("k", 4, 64), ("v", 4, 32))`` keys and values of different widths. Every tensor
+    of a request is laid out [num_pages, heads, page_size, width] in the compute dtype and shares the request's
+    page ids, so one block table and one slot mapping serve them all.
+    """
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None     # None: every token is kept
+    tensors: tuple = ()              # of (name, heads, width); empty: ("k", ...) and ("v", ...) of the plain form
+
+    def layout(self) -> tuple:
+        if self.tensors:
+            return tuple((str(n), int(h), int(w)) for n, h, w in self.tensors)
+        return (("k", int(self.num_kv_heads), int(self.head_dim)), ("v", int(self.num_kv_heads), int(self.head_dim)))
+
+    def elements_per_token(self) -> int:
+        return sum(h * w for _n, h, w in self.layout())
 
 
 @dataclass(frozen=True)
@@ -151,5 +172,25 @@ class Layer(Part):
         raise NotImplementedError
 
 
-__all__ = ["CATEGORIES", "register_part", "build_part", "registered_parts", "CacheRequest", "StateRequest", "Part", "Norm",
+class Embedding(Part):
+    def forward(self, ctx, out) -> None:
+        """``out`` (float32 [tokens, hidden], the residual stream) from ``ctx.token_ids[:tokens]``; rows whose
+        ``ctx.seq_of_token`` is -1 are padding."""
+        raise NotImplementedError
+
+    def table(self):
+        """The [vocab, hidden] matrix that a head without a tensor of its own multiplies by, or None."""
+        return None
+
+
+class Head(Part):
+    def bind(self, weights: dict, tied=None) -> None:
+        """``tied``: the embedding's ``table()`` when the head's spec names no tensor."""
+
+    def forward(self, x, out) -> None:
+        """``out`` (float32 [rows, vocab]) from the normed rows ``x`` [rows, hidden]."""
+        raise NotImplementedError
+
+
+__all__ = ["CATEGORIES", "Embedding", "Head", "register_part", "build_part", "registered_parts", "CacheRequest", "StateRequest", "Part", "Norm",
            "PositionEncoding", "Mixer", "FeedForward", "Layer", "TensorDecl", "Projection"]

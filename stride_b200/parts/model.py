@@ -1,5 +1,6 @@
 """A decoder put together from a ``ModelSpec``: embedding, layers run in the
-order that the spec's schedule gives, final norm, output head.
+order that the spec's schedule gives, final norm, output head; each of them a
+part chosen by its spec's kind.
 
 The schedule is data: an entry names a layer and a cache slot, so a layer may
 run twice (with two slots, or sharing one) and a run may read the keys and
@@ -13,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from ..weights import TensorDecl, load_weights
+from ..weights import load_weights
 from .base import build_part
 from .runtime import ResidualStream, Runtime
 
@@ -23,43 +24,41 @@ class DecoderModel:
         self.spec = spec
         self.rt = runtime
         self.hidden, self.vocab = spec.hidden, spec.vocab
+        self.embedding = build_part("embedding", spec.embedding_spec(), runtime)
         self.layers = [build_part("layer", ls, runtime) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
+        self.head = build_part("head", spec.head_spec(), runtime)
         self.schedule = tuple(spec.schedule)
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"the schedule names layer {e.layer}, but there are {len(self.layers)} layers")
-        self.embed = self.head = None
         self.caches = None          # list of LayerCache, one per schedule entry; set by DeviceCache.attach
         self.capture = None         # when a list, every run appends the float32 hidden state (diagnostics)
 
     # ----------------------------------------------------------------- weights
+    def _parts(self):
+        return [self.embedding, *self.layers, self.final_norm, self.head]
+
     def declare(self) -> dict:
-        d = {self.spec.embed_name: TensorDecl((self.vocab, self.hidden))}
-        if self.spec.head_name is not None:
-            d[self.spec.head_name] = TensorDecl((self.vocab, self.hidden))
-        for layer in self.layers:
-            d.update(layer.declare())
-        d.update(self.final_norm.declare())
+        d = {}
+        for part in self._parts():
+            d.update(part.declare())
         return d
 
     def load(self, source) -> None:
         """Reads every declared tensor from ``source`` (checked first; one error
         lists all that is missing, unexpected or mis-shaped) and hands them out."""
         weights = load_weights(source, self.declare(), self.rt.dtype, self.rt.device, self.spec.ignorable_tensors)
-        self.embed = weights[self.spec.embed_name]
-        self.head = weights[self.spec.head_name] if self.spec.head_name is not None else self.embed
+        self.embedding.bind(weights)
         for layer in self.layers:
             layer.bind(weights)
         self.final_norm.bind(weights)
+        self.head.bind(weights, tied=self.embedding.table())
 
     def named_tensors(self) -> dict:
-        d = {self.spec.embed_name: self.embed}
-        if self.spec.head_name is not None:
-            d[self.spec.head_name] = self.head
-        for layer in self.layers:
-            d.update(layer.named_tensors())
-        d.update(self.final_norm.named_tensors())
+        d = {}
+        for part in self._parts():
+            d.update(part.named_tensors())
         return d
 
     def get_weight(self, name: str) -> torch.Tensor:
@@ -97,7 +96,9 @@ class DecoderModel:
             raise RuntimeError("the model has no cache attached")
         tokens = ctx.num_tokens
         stream = ResidualStream(self.rt, tokens, self.hidden)
-        ops.embed_gather(ctx.token_ids[:tokens], ctx.seq_of_token[:tokens], self.embed, stream.residual)
+        self.embedding.forward(ctx, stream.residual)
+        for state in self._states():        # a request that starts in this step finds its state slots at zero
+            ops.zero_fresh_state(state, ctx.state_slot, ctx.q_start, ctx.q_len, ctx.positions)
         for entry, cache in zip(self.schedule, self.caches):
             self.layers[entry.layer].forward(stream, ctx, cache)
             if self.capture is not None:
@@ -111,8 +112,17 @@ class DecoderModel:
         logits = self.rt.buffer("logits", rows, self.vocab, torch.float32, row_kind="rows")
         if rows:
             normed = stream.normed(self.final_norm, rows=ctx.logit_rows[:rows])
-            ops.linear(normed, self.head, logits)
+            self.head.forward(normed, logits)
         return logits
+
+    def _states(self) -> list:
+        """The per-request state tensors of the attached cache, each once."""
+        seen, out = set(), []
+        for cache in self.caches or ():
+            if cache.state is not None and id(cache.state) not in seen:
+                seen.add(id(cache.state))
+                out.append(cache.state)
+        return out
 
     @property
     def graph_safe(self) -> bool:

@@ -62,5 +62,5 @@ def test_the_diagnose_command_line(probe_case):
     proc = subprocess.run([sys.executable, "-m", "stride_b200", "diagnose", "prefill", "--model", folder, "--dtype", dtype,
                            "--tokens", "100", "--chunk", "5,64"], cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout + proc.stderr
-    assert "chunk=5: EQUIVALENT" in proc.stdout and "chunk=64: EQUIVALENT" in proc.stdout
+    assert "chunk=5 [same]" in proc.stdout and "chunk=64 [same]" in proc.stdout
     assert "Portions match the whole prompt." in proc.stdout

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.fixture(scope="module", params=["A", "B"])
+@pytest.fixture(scope="module", params=["A", "B", "D"])
 def case(request, tmp_models):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
@@ -28,10 +28,12 @@ def case(request, tmp_models):
     for dtype, stored in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
         out["dirs"][dtype] = write_model_dir(str(tmp_models / f"gen_{name}_{dtype}"), cfg, state, stored)
         out["state"][dtype] = read_model_dir(out["dirs"][dtype])[1]
-    lengths = [1, 7, 16, 33] if name == "A" else [3, 25, 41, 57, 72, 90]
-    shared = seeded_tokens(24, cfg["vocab_size"], 500)
-    out["prompts"] = [(shared[:min(24, n - 1)] + seeded_tokens(n, cfg["vocab_size"], 501 + i))[:n] if name == "B"
-                      else seeded_tokens(n, cfg["vocab_size"], 501 + i) for i, n in enumerate(lengths)]
+    # B and D: prompts that share their first tokens (24 and 40: more than a page, so that later requests find pages
+    # of earlier ones in the prefix index); D has the head size and group that the tensor-core kernels take
+    lengths = {"A": [1, 7, 16, 33], "B": [3, 25, 41, 57, 72, 90], "D": [3, 41, 57, 72, 90, 150]}[name]
+    common = {"A": 0, "B": 24, "D": 40}[name]
+    shared = seeded_tokens(common, cfg["vocab_size"], 500)
+    out["prompts"] = [(shared[:min(common, n - 1)] + seeded_tokens(n, cfg["vocab_size"], 501 + i))[:n] for i, n in enumerate(lengths)]
     out["new_tokens"] = 8 if name == "A" else 12
     return out
 
@@ -80,22 +82,146 @@ def test_greedy_generation_through_the_entry_point(case, dtype):
         assert m["prefill_tokens_reused"] > 0, "the shared 24-token prefix was never found in the cache"
 
 
-def test_small_budgets_small_pools_and_resume_give_the_same_tokens(case):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_budgets_small_pools_and_resume_give_the_same_tokens(case, dtype):
     """Portions of 5..16 tokens, a pool that cannot hold every request, so that
-    requests are preempted and recomputed, with and without the prefix index."""
+    requests are preempted and recomputed, with and without the prefix index. In
+    bfloat16 (on the configuration whose sizes the tensor-core kernels take: prefill
+    attention on tcgen05 reads a prefix that another request wrote, decode attention
+    resumes after a preemption) every token is checked against the plain logits of
+    the sequence the engine produced."""
     from stride_b200 import SamplingParams
+    if dtype == "bfloat16" and case["name"] != "D":
+        pytest.skip("bfloat16 runs on the configuration that takes the tensor-core kernels")
     n = case["new_tokens"] + 20
-    want = [plain.greedy_generate(case["cfg"], case["state"]["float32"], p, n, torch.float64) for p in case["prompts"]]
+    if dtype == "float32":
+        want = [plain.greedy_generate(case["cfg"], case["state"]["float32"], p, n, torch.float64) for p in case["prompts"]]
     longest = max(len(p) for p in case["prompts"]) + n
     pages = -(-longest // case["page"]) + 3
     for prefix_caching in (True, False):
-        engine = engine_for(case, "float32", num_blocks=pages, max_batch_tokens=16, max_batch_seqs=4, watermark=0.0,
+        engine = engine_for(case, dtype, num_blocks=pages, max_batch_tokens=16, max_batch_seqs=4, watermark=0.0,
                             prefix_caching=prefix_caching)
         outs = engine.generate(case["prompts"], SamplingParams(temperature=0.0, max_tokens=n))
-        assert [o.tokens for o in outs] == want
+        if dtype == "float32":
+            assert [o.tokens for o in outs] == want
+        else:
+            for prompt, out in zip(case["prompts"], outs):
+                assert len(out.tokens) == n
+                assert_greedy(case, dtype, prompt, out.tokens, f"prompt of {len(prompt)}, prefix index {prefix_caching}")
         m = engine.metrics()
         assert m["preemptions"] > 0, "the pool was meant to be too small"
         assert m["kv_blocks_live"] == 0
+        if prefix_caching and case["name"] != "A":
+            assert m["prefill_tokens_reused"] > 0, "no request found the shared prefix in the index"
+
+
+def test_a_poisoned_shared_prefix_shows(case):
+    """Negative control of the prefix tests: when the pages that a finished request left in the index are
+    overwritten, a later request that adopts them must produce other tokens. If it did not, the tests above could
+    not tell whether shared pages are read at all."""
+    from stride_b200 import SamplingParams
+    if case["name"] == "A":
+        pytest.skip("the prompts of this configuration share no prefix")
+    dtype = "bfloat16" if case["name"] == "D" else "float32"
+    engine = engine_for(case, dtype)
+    params = SamplingParams(temperature=0.0, max_tokens=6)
+    first, second = case["prompts"][-2], case["prompts"][-1]
+    engine.generate([first], params)
+    assert engine.cache_stats()["cached"] > 0
+    for pages in engine.device_cache.pages:       # every page: the live ones are none, the cached ones hold the prefix
+        pages.normal_(0.0, 3.0)
+    out = engine.generate([second], params)[0]
+    assert out.cached_prompt_tokens >= case["page"], "the second request did not adopt the first one's pages"
+    with pytest.raises(AssertionError):
+        assert_greedy(case, dtype, second, out.tokens, "poisoned prefix")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(case, dtype):
+    """Decode steps are launched before the tokens of the step before them are read (their token ids travel on the
+    device). With that switched off every step waits for its tokens first; both must produce the same tokens and
+    events, also for requests that stop on a token in the middle of such a chain, draw with a temperature, or
+    reach their limit."""
+    from stride_b200 import SamplingParams
+    prompts = case["prompts"][-3:]
+    free = engine_for(case, dtype, chain_steps=False).generate(prompts[:1], SamplingParams(temperature=0.0, max_tokens=24))[0].tokens
+    stop_at = free[10]
+    params = [SamplingParams(temperature=0.0, max_tokens=24, stop_tokens=[stop_at]), SamplingParams(temperature=0.9, max_tokens=30, seed=11),
+              SamplingParams(temperature=0.0, max_tokens=17)]
+    runs = {}
+    for chain in (False, True):
+        engine = engine_for(case, dtype, chain_steps=chain, prefix_caching=False)
+        ids = [engine.add_request(p, sp) for p, sp in zip(prompts, params)]
+        events = []
+        while engine.has_unfinished():
+            events += engine.step()
+        m = engine.metrics()
+        assert (m["chained_steps"] > 5) == chain, m
+        assert m["kv_blocks_live"] == 0
+        runs[chain] = ([(engine.output(i).tokens, engine.output(i).finish_reason) for i in ids], sorted(events, key=lambda e: e[0]))
+    assert runs[True][0][0] == (free[:free.index(stop_at)], "stop")
+    assert runs[True] == runs[False]
+
+
+def test_a_failed_kernel_wait_ends_the_step_with_an_error_and_the_engine_goes_on(case):
+    """A wait inside a kernel that cannot be satisfied runs into its limit, records a code in the status word and
+    returns (a kernel of this test does exactly that, with a limit of microseconds, on an mbarrier that nothing
+    completes). The step whose results come back with that word raises, its requests end with the reason "error",
+    the word is cleared, and a request added afterwards runs as if nothing had happened."""
+    import ctypes
+    from stride_b200 import SamplingParams
+    from stride_b200.csrc import build, ops
+    lib = build.load_external_library(os.path.join(ROOT, "tests", "kernels", "wait_runs_out.cu"))
+    lib.test_wait_runs_out.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
+    lib.test_wait_runs_out.restype = ctypes.c_int
+    engine = engine_for(case, "float32")
+    status = ops.status_tensor("cuda")
+    returned = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+
+    def run_out(code):
+        rc = lib.test_wait_runs_out(status.data_ptr(), code, 100000, returned.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(returned[0]) == 0, "the wait reported success on a barrier that nothing completes"
+
+    # the word by itself: read, reported once, cleared
+    run_out(3)
+    with pytest.raises(ops.KernelError, match="code 3: matrix product: epilogue"):
+        ops.check_kernel_status()
+    ops.check_kernel_status()
+    # through the engine
+    params = SamplingParams(temperature=0.0, max_tokens=4)
+    doomed = engine.add_request(case["prompts"][1], params)
+    run_out(2)
+    with pytest.raises(ops.KernelError, match="code 2"):
+        engine.step()
+    out = engine.output(doomed)
+    assert out.finished and out.finish_reason == "error" and not engine.has_unfinished()
+    assert engine.cache_stats()["live"] == 0 and engine.cache_stats()["cached"] == 0, "pages of a failed step must not be shared"
+    after = engine.generate([case["prompts"][1]], params)[0]
+    assert after.finish_reason == "length"
+    assert after.tokens == plain.greedy_generate(case["cfg"], case["state"]["float32"], case["prompts"][1], 4, torch.float64)
+
+
+def test_a_position_beyond_the_position_tables_is_refused_on_the_host(tmp_models):
+    """max_position_embeddings 100 with pages of 16: the block table reaches 112 positions, the rotation tables end
+    at 100. The raw step function must refuse position 100 before any kernel reads the tables."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from stride_b200 import Engine
+    cfg = dict(TINY["A"], max_position_embeddings=100)
+    folder = write_model_dir(str(tmp_models / "short_tables"), cfg, seeded_state(cfg, 3), torch.float32)
+    engine = Engine(folder, dtype="float32", block_size=16, num_blocks=16, max_model_len=4096)
+    assert engine.max_model_len == 100
+    engine.cache.open(7, "t")
+    assert engine.cache.ensure(7, 112, 0)
+    tokens = seeded_tokens(100, cfg["vocab_size"], 1)
+    assert engine.forward([(7, tokens, 0, [99])]).shape == (1, cfg["vocab_size"])
+    with pytest.raises(ValueError, match="position 100"):
+        engine.forward([(7, [5], 100, [0])])
+    with pytest.raises(ValueError, match="max_model_len is 100"):
+        engine.forward([(7, tokens[:12], 95, [0])])
+    engine.cache.close(7)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

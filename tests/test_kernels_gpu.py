@@ -410,6 +410,30 @@ def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
     assert not ops.fast_attention_supported(torch.float32, 4, 2, 128)
 
 
+def test_decode_attention_refuses_a_position_beyond_the_bound_of_its_launch(ops):
+    """A launch is sized for positions below ``max_context``. A row beyond it would wait for splits that were never
+    launched; it gets zeros and a code in the status word instead, and leaves no ticket behind: the next launch on
+    the same scratch is right."""
+    g = torch.Generator().manual_seed(21)
+    dtype, nq, nkv, hd, page = torch.bfloat16, 8, 2, 128, 16
+    seqs = [(300, 1), (1100, 1), (40, 1)]
+    q, k_pages, v_pages, table, seq_of, pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page)
+    scratch = torch.zeros(ops.decode_scratch_floats(q.shape[0], nq, nkv, hd, 2048), device="cuda")
+    args = (dev(k_pages), dev(v_pages), dev(table), dev(seq_of), dev(pos), scratch, nq, nkv, hd, page, hd ** -0.5, 0)
+    ops.check_kernel_status()
+    out = torch.full((3, nq * hd), 5.0, dtype=dtype, device="cuda")
+    ops.paged_attention_decode(dev(q), nq * hd, out, *args, 1024)          # the second row sits at position 1100
+    with pytest.raises(ops.KernelError, match="context bound"):
+        ops.check_kernel_status()
+    ops.check_kernel_status()                                              # reported once, then cleared
+    assert float(out[1].abs().max()) == 0.0
+    close(out[[0, 2]], want[[0, 2]], dtype)
+    assert int(scratch[:65536].view(torch.int32).abs().max()) == 0, "the refused row left a ticket behind"
+    ops.paged_attention_decode(dev(q), nq * hd, out, *args, 1024 + 128)
+    close(out, want, dtype)
+    ops.check_kernel_status()
+
+
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(8, 2, 128, 16, None), (4, 1, 64, 32, None), (8, 2, 128, 16, 3000)])
 def test_decode_attention_long_contexts(ops, nq, nkv, hd, page, window):
     """Tens of splits of up to 1,024 keys, each walked in many tiles; one far key per request carries nearly all

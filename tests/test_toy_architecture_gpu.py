@@ -26,8 +26,10 @@ def register_toy():
     from stride_b200.parts import Mixer, StateRequest, TensorDecl, register_part
 
     class RunningMeanMixer(Mixer):
-        """delta_t = W * mean(x_0 .. x_t); the sum so far is per-request state."""
-        graph_safe = False          # it walks the host's list of the step's requests
+        """delta_t = W * mean(x_0 .. x_t); the sum so far is per-request state. Everything it needs of the step it
+        takes from the step's arrays on the device (which sequence a token belongs to, where a sequence starts, its
+        state slot), so a step that holds it can be captured in a graph and replayed. The framework hands out the
+        slot and clears it when a request starts."""
 
         def declare(self):
             h = self.spec.hidden
@@ -40,14 +42,21 @@ def register_toy():
             return StateRequest((self.spec.hidden,), torch.float32)
 
         def forward(self, x, ctx, cache):
-            out = self.rt.buffer("toy_mixer_out", x.shape[0], self.spec.hidden)
-            for _request, row, n, position, slot in ctx.host_items:
-                if position == 0:
-                    cache.state[slot].zero_()
-                sums = torch.cumsum(x[row: row + n].float(), 0) + cache.state[slot]
-                cache.state[slot].copy_(sums[-1])
-                counts = torch.arange(position + 1, position + n + 1, device=x.device, dtype=torch.float32).unsqueeze(1)
-                out[row: row + n] = ((sums / counts).to(x.dtype).float() @ self.w.float().t()).to(x.dtype)
+            n = x.shape[0]
+            seq = ctx.seq_of_token[:n].long()                   # -1: a padded row
+            live = (seq >= 0).unsqueeze(1)
+            seq = seq.clamp(min=0)
+            start, count, slot = ctx.q_start.long(), ctx.q_len.long(), ctx.state_slot.long()
+            running = torch.cumsum(torch.where(live, x.double(), 0.0), 0)                   # over the flat batch
+            before = torch.where((start > 0).unsqueeze(1), running[(start - 1).clamp(min=0)], 0.0)      # [sequences, h]
+            within = running - before[seq]                      # sum over the sequence's tokens of this step so far
+            sums = within + cache.state[slot[seq]].double()
+            mean = (sums / (ctx.positions[:n] + 1).double().unsqueeze(1)).to(x.dtype)
+            # the state grows by the sum of the step's tokens; padded sequences (count 0) add nothing, whatever slot they name
+            last = (start + count - 1).clamp(min=0)
+            cache.state.index_add_(0, slot, torch.where((count > 0).unsqueeze(1), within[last], 0.0).float())
+            out = self.rt.buffer("toy_mixer_out", n, self.spec.hidden)
+            out.copy_((mean.float() @ self.w.float().t()).to(x.dtype))
             return out
 
     @dataclass(frozen=True)
@@ -141,12 +150,15 @@ def test_a_toy_architecture_with_a_stateful_mixer_runs_through_the_engine(tmp_mo
     requests = {r: seeded_tokens(n, TOY["vocab_size"], 900 + i) for i, (r, n) in enumerate({"a": 60, "b": 23, "c": 41, "d": 9}.items())}
     want = {r: plain_toy(state, t) for r, t in requests.items()}
     tol = "float32" if dtype == "float32" else "bfloat16"
+    replays = 0
     for name, steps in (("whole", modes.whole(requests)), ("portions", modes.changing_portions(requests)),
-                        ("mixed", modes.mixed(requests, live_limit=3, seed=4))):
+                        ("tail", modes.tail_one_by_one(requests, tail=12)), ("mixed", modes.mixed(requests, live_limit=3, seed=4))):
         session = TraceSession(folder, dtype, max_tokens=modes.peak_tokens(steps), block_size=8)
         assert len(session.device_cache.groups) == 1 and session.device_cache.groups[0].window == TOY["window"]
         assert session.device_cache.groups[0].slots == (0, 2) and list(session.device_cache.states) == [1]
-        assert not session.runner.cuda_graphs, "a part that reads the host's view of a step must not be graph-replayed"
+        assert session.runner.cuda_graphs, "a mixer with state that reads the step from the device can be graph-replayed"
+        for state in session.device_cache.states.values():      # whatever a slot held before: a new request starts at zero
+            state.fill_(float("nan"))
         rows = modes.expected_rows(steps)
         for s in steps:
             out = session.run_step(s)
@@ -155,8 +167,12 @@ def test_a_toy_architecture_with_a_stateful_mixer_runs_through_the_engine(tmp_mo
                 assert ok, f"{name}: request {rid!r} position {pos}: {msg}"
         stats = session.cache.stats()
         assert stats["live"] == 0 and session.cache.free_slots == session.cache.slot_capacity
+        replays += session.runner.graph_replays
         if name == "whole":
             assert stats["capacity"] * 8 >= 64, "sanity"
+        if name == "tail":
+            assert session.runner.graph_replays >= 40, "the single-token steps did not go through captured graphs"
+    assert replays > 0
 
 
 # --------------------------------------------------------------------------------------------------------------
@@ -390,5 +406,174 @@ def test_a_toy_architecture_of_foreign_parts_runs_through_the_engine(tmp_models)
             out = session.run_step(s)
             for r, (rid, pos) in enumerate(rows[s["step"]]):
                 ok, msg = compare_logits(out[r:r + 1], want[rid][pos:pos + 1], "float32")
+                assert ok, f"{name}: request {rid!r} position {pos}: {msg}"
+        assert session.cache.stats()["live"] == 0
+
+
+# --------------------------------------------------------------------------------------------------------------
+# A third toy: the two ends of the model and what the mixer keeps in pages come from this file. The embedding is a
+# table lookup times sqrt(width); the head adds a bias and caps the logits with a tanh; the mixer keeps ONE vector of
+# 24 numbers per token in the pages (not keys and values), attends over those vectors and projects the weighted
+# vector back. Norms, feed-forward, arrangement, cache manager and step function are the package's.
+LATENT = {"architectures": ["ToyLatentLM"], "hidden_size": 56, "vocab_size": 101, "intermediate_size": 72, "latent": 24, "eps": 1e-5,
+          "cap": 4.0, "max_positions": 160, "layers": 2}
+
+
+def register_latent_toy():
+    from dataclasses import dataclass
+
+    from stride_b200.config import (EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, ScheduleEntry,
+                                    register_architecture)
+    from stride_b200.parts import CacheRequest, Embedding, Head, Mixer, TensorDecl, register_part
+
+    class ScaledLookup(Embedding):
+        def declare(self):
+            return {self.spec.name: TensorDecl((self.spec.vocab, self.spec.hidden))}
+
+        def bind(self, weights):
+            self.weight = weights[self.spec.name]
+
+        def forward(self, ctx, out):
+            n = out.shape[0]
+            live = (ctx.seq_of_token[:n] >= 0).unsqueeze(1)
+            rows = self.weight[ctx.token_ids[:n].long()].float() * dict(self.spec.params)["multiplier"]
+            out.copy_(torch.where(live, rows, 0.0))
+
+    class CappedHead(Head):
+        def declare(self):
+            return {self.spec.name: TensorDecl((self.spec.vocab, self.spec.hidden)),
+                    self.spec.name.replace("weight", "bias"): TensorDecl((self.spec.vocab,), "vector")}
+
+        def bind(self, weights, tied=None):
+            self.weight, self.bias = weights[self.spec.name], weights[self.spec.name.replace("weight", "bias")]
+
+        def forward(self, x, out):
+            cap = dict(self.spec.params)["cap"]
+            out.copy_(cap * torch.tanh((x.float() @ self.weight.float().t() + self.bias) / cap))
+
+    class LatentMixer(Mixer):
+        """c_t = Wc x_t is what a token leaves in the cache; delta_t = Wo sum_j softmax_j(q_t . c_j / sqrt(r)) c_j over j <= t."""
+        graph_safe = False          # it walks the host's list of the step's requests
+
+        def declare(self):
+            h, r, p = self.spec.hidden, dict(self.spec.params)["latent"], self.spec.prefix
+            return {p + "c.weight": TensorDecl((r, h)), p + "q.weight": TensorDecl((r, h)), p + "o.weight": TensorDecl((h, r))}
+
+        def bind(self, weights):
+            p = self.spec.prefix
+            self.wc, self.wq, self.wo = weights[p + "c.weight"], weights[p + "q.weight"], weights[p + "o.weight"]
+
+        def cache_request(self):
+            return CacheRequest(tensors=(("latent", 1, dict(self.spec.params)["latent"]),))
+
+        def forward(self, x, ctx, cache):
+            r = self.wc.shape[0]
+            pages = cache.tensors["latent"]                             # [num_pages, 1, page_size, r]
+            flat = pages.view(-1, r)                                    # one head: row = page * page_size + offset
+            n = x.shape[0]
+            c = (x.float() @ self.wc.float().t()).to(x.dtype)
+            q = (x.float() @ self.wq.float().t()).to(x.dtype).float()
+            slots = ctx.slot_mapping[cache.group][:n].long()
+            live = slots >= 0
+            flat[slots[live]] = c[live]
+            out = self.rt.buffer("toy_latent_out", n, self.spec.hidden)
+            out.zero_()
+            table = ctx.block_table[cache.group]
+            for index, (_request, row, count, position, _slot) in enumerate(ctx.host_items):
+                end = position + count
+                at = torch.arange(end, device=x.device)
+                kept = flat[table[index, at // cache.page_size].long() * cache.page_size + at % cache.page_size].float()      # [end, r]
+                scores = q[row:row + count] @ kept.t() * r ** -0.5
+                mask = at.unsqueeze(0) > (position + torch.arange(count, device=x.device)).unsqueeze(1)
+                weights = torch.softmax(scores.masked_fill(mask, float("-inf")), -1)
+                out[row:row + count] = ((weights @ kept).to(x.dtype).float() @ self.wo.float().t()).to(x.dtype)
+            return out
+
+    @dataclass(frozen=True)
+    class LatentConfig:
+        d: tuple
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in d.items())))
+
+        def to_dict(self):
+            return {k: (list(v) if isinstance(v, tuple) else v) for k, v in self.d}
+
+        def to_model_spec(self):
+            c = self.to_dict()
+            h = c["hidden_size"]
+            norm = lambda p: NormSpec("rmsnorm", h, c["eps"], p)
+            layers = tuple(LayerSpec("pre_norm", MixerSpec("toy_latent", hidden=h, prefix=f"toy.layers.{l}.mix.", params=(("latent", c["latent"]),)),
+                                     FeedForwardSpec("swiglu", hidden=h, intermediate=c["intermediate_size"], prefix=f"toy.layers.{l}.mlp."),
+                                     norm(f"toy.layers.{l}.n1."), norm(f"toy.layers.{l}.n2.")) for l in range(c["layers"]))
+            return ModelSpec("ToyLatentLM", h, c["vocab_size"], layers, tuple(ScheduleEntry(l, l) for l in range(c["layers"])),
+                             norm("toy.norm."), "toy.embed.weight", "toy.head.weight", c["max_positions"],
+                             embedding=EmbeddingSpec("toy_scaled_lookup", c["vocab_size"], h, "toy.embed.weight", (("multiplier", h ** 0.5),)),
+                             head=HeadSpec("toy_capped", c["vocab_size"], h, "toy.head.weight", (("cap", c["cap"]),)))
+
+    register_part("embedding", "toy_scaled_lookup", ScaledLookup)
+    register_part("head", "toy_capped", CappedHead)
+    register_part("mixer", "toy_latent", LatentMixer)
+    register_architecture("ToyLatentLM", LatentConfig)
+
+
+def latent_state(seed):
+    g = torch.Generator().manual_seed(seed)
+    c, h, r, i = LATENT, LATENT["hidden_size"], LATENT["latent"], LATENT["intermediate_size"]
+    m = lambda rows, cols, s=0.15: torch.randn(rows, cols, generator=g) * s
+    v = lambda: 1 + 0.1 * torch.randn(h, generator=g)
+    s = {"toy.embed.weight": m(c["vocab_size"], h, 0.1), "toy.head.weight": m(c["vocab_size"], h, 0.3),
+         "toy.head.bias": torch.randn(c["vocab_size"], generator=g) * 0.5, "toy.norm.weight": v()}
+    for l in range(c["layers"]):
+        p = f"toy.layers.{l}."
+        s.update({p + "mix.c.weight": m(r, h, 0.12), p + "mix.q.weight": m(r, h, 0.12), p + "mix.o.weight": m(h, r), p + "n1.weight": v(),
+                  p + "n2.weight": v(), p + "mlp.gate_proj.weight": m(i, h), p + "mlp.up_proj.weight": m(i, h),
+                  p + "mlp.down_proj.weight": m(h, i)})
+    return s
+
+
+def plain_latent(state, tokens):
+    w = {k: t.double() for k, t in state.items()}
+    c = LATENT
+    n, r = len(tokens), c["latent"]
+    x = w["toy.embed.weight"][torch.tensor(tokens)] * c["hidden_size"] ** 0.5
+    for l in range(c["layers"]):
+        p = f"toy.layers.{l}."
+        h = plain.rms_norm(x, w[p + "n1.weight"], c["eps"])
+        kept, q = h @ w[p + "mix.c.weight"].T, h @ w[p + "mix.q.weight"].T
+        scores = (q @ kept.T * r ** -0.5).masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool), 1), float("-inf"))
+        x = x + torch.softmax(scores, -1) @ kept @ w[p + "mix.o.weight"].T
+        h = plain.rms_norm(x, w[p + "n2.weight"], c["eps"])
+        x = x + plain.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    logits = plain.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.head.weight"].T + w["toy.head.bias"]
+    return c["cap"] * torch.tanh(logits / c["cap"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_with_its_own_ends_and_one_cached_vector_per_token_runs_through_the_engine(tmp_models, dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from stride_b200.engine.trace import TraceSession
+    register_latent_toy()
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    state = latent_state(9)
+    folder = write_model_dir(str(tmp_models / f"toy_latent_{dtype}"), LATENT, state, stored)
+    state = {k: v.to(stored) for k, v in state.items()}
+    requests = {r: seeded_tokens(n, LATENT["vocab_size"], 800 + i) for i, (r, n) in enumerate({"a": 70, "b": 19, "c": 44, "d": 5}.items())}
+    want = {r: plain_latent(state, t) for r, t in requests.items()}
+    for name, steps in (("whole", modes.whole(requests)), ("tail", modes.tail_one_by_one(requests, tail=10)),
+                        ("portions", modes.changing_portions(requests)), ("mixed", modes.mixed(requests, live_limit=3, seed=6))):
+        session = TraceSession(folder, dtype, max_tokens=modes.peak_tokens(steps), block_size=8)
+        group = session.device_cache.groups[0]
+        assert group.layout == (("latent", 1, LATENT["latent"]),) and group.slots == (0, 1)
+        assert [tuple(t.shape[2:]) for t in session.device_cache.pages] == [(1, 8, LATENT["latent"])], "one vector per token is kept"
+        for pages in session.device_cache.pages:
+            pages.fill_(float("nan"))
+        rows = modes.expected_rows(steps)
+        for s in steps:
+            out = session.run_step(s)
+            for r, (rid, pos) in enumerate(rows[s["step"]]):
+                ok, msg = compare_logits(out[r:r + 1], want[rid][pos:pos + 1], dtype)
                 assert ok, f"{name}: request {rid!r} position {pos}: {msg}"
         assert session.cache.stats()["live"] == 0
