@@ -22,10 +22,12 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 
-from helpers import PAGE_SIZE, TINY, seeded_state, seeded_tokens  # noqa: E402
+from helpers import PAGE_SIZE, TINY, seeded_biases, seeded_state, seeded_tokens  # noqa: E402
 
-GOLDEN_SEED = {"A": 11, "B": 22, "C": 33}
-GOLDEN_TOKENS = {"A": 40, "B": 90, "C": 37}
+# "A_bias": configuration A from a checkpoint that has q/k/v projection biases (the reference adds them when the
+# tensors are there, python/stride_worker/model.py:159-169)
+GOLDEN_SEED = {"A": 11, "B": 22, "C": 33, "A_bias": 44}
+GOLDEN_TOKENS = {"A": 40, "B": 90, "C": 37, "A_bias": 40}
 
 
 def main(reference_python: str) -> None:
@@ -34,11 +36,14 @@ def main(reference_python: str) -> None:
     from stride_worker.model import StrideModel
     from stride_worker.protocol import SequenceWork
 
-    for name, cfg in TINY.items():
+    for name in GOLDEN_SEED:
+        cfg = TINY[name.split("_")[0]]
         state = seeded_state(cfg, GOLDEN_SEED[name])
+        if name.endswith("_bias"):
+            state.update(seeded_biases(cfg, GOLDEN_SEED[name] + 2))
         tokens = seeded_tokens(GOLDEN_TOKENS[name], cfg["vocab_size"], GOLDEN_SEED[name] + 1)
         model = StrideModel(dict(cfg), state, torch.device("cpu"), torch.float32)
-        page = PAGE_SIZE[name]
+        page = PAGE_SIZE[name.split("_")[0]]
         pages_needed = (len(tokens) + page - 1) // page
         cache = PagedKVCache(model.cache_spec(2 * pages_needed + 3, page))
         blocks = [2 * i + 1 for i in range(pages_needed)][::-1]

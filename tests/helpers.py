@@ -147,6 +147,18 @@ def seeded_state(cfg: dict, seed: int, std: float = 0.02, norm_jitter: float = 0
     return state
 
 
+def seeded_biases(cfg: dict, seed: int, std: float = 0.1) -> dict:
+    """q/k/v projection biases N(0, std) for every layer (the reference uses them when the checkpoint has them,
+    python/stride_worker/model.py:159-169)."""
+    g = torch.Generator().manual_seed(seed)
+    nq, nkv, hd = geometry(cfg)
+    out = {}
+    for i in range(int(cfg["num_hidden_layers"])):
+        for proj, rows in (("q", nq * hd), ("k", nkv * hd), ("v", nkv * hd)):
+            out[f"model.layers.{i}.self_attn.{proj}_proj.bias"] = torch.randn(rows, generator=g, dtype=torch.float32) * std
+    return out
+
+
 def seeded_tokens(n: int, vocab: int, seed: int) -> list[int]:
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()

@@ -8,17 +8,19 @@ import pytest
 import torch
 
 import plain_llama as plain
-from helpers import TINY, compare_logits, seeded_state, seeded_tokens
+from helpers import TINY, compare_logits, seeded_biases, seeded_state, seeded_tokens
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
-GOLDEN_SEED = {"A": 11, "B": 22, "C": 33}
-GOLDEN_TOKENS = {"A": 40, "B": 90, "C": 37}
+GOLDEN_SEED = {"A": 11, "B": 22, "C": 33, "A_bias": 44}
+GOLDEN_TOKENS = {"A": 40, "B": 90, "C": 37, "A_bias": 40}
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "A_bias"])
 def test_plain_matches_reference_model(name):
-    cfg = TINY[name]
+    cfg = TINY[name.split("_")[0]]
     state = seeded_state(cfg, GOLDEN_SEED[name])
+    if name.endswith("_bias"):      # a checkpoint with q/k/v biases: the reference adds them because the tensors are there
+        state.update(seeded_biases(cfg, GOLDEN_SEED[name] + 2))
     tokens = seeded_tokens(GOLDEN_TOKENS[name], cfg["vocab_size"], GOLDEN_SEED[name] + 1)
     want = torch.from_numpy(np.load(os.path.join(GOLDEN, f"tiny_{name}.npy")))
     got = plain.forward(cfg, state, tokens, torch.float32)
