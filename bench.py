@@ -15,7 +15,11 @@ a batch of 8 requests at a context of 8192 tokens. It prints ONE JSON line:
   bf16 matrix peak;
 * ``roofline``: bytes the decode step has to read divided by its time, against
   the measured copy bandwidth;
-* ``points``: decode at batch 1 and 64.
+* ``points``: decode at batch 1 and 64 at the run's context, and at batch 1, 8 and
+  64 at a context of 2,048 (``--points`` chooses other batches; the page pool is
+  sized for what the run holds at once);
+* ``breakdown``: device time per class of kernel of one decode step and of the
+  prefill, from CUDA events around every launch of an eagerly run step.
 
 Peaks come from MEASURED_PEAKS.json when the file exists, else from an earlier
 measurement on the same pool (6.65 TB/s, 1.59 PFLOP/s). ``--impl reference``
@@ -180,6 +184,54 @@ def _time_graph(engine, step_batch, steps: int, warmup: int):
     return ms / steps, clocks.summary, runner.replayed_launches - launches_before
 
 
+def _rounded(milliseconds: dict, keep: int = 14) -> dict:
+    """The largest classes in microseconds, the rest summed up."""
+    items = list(milliseconds.items())
+    out = {k: round(v * 1e3) for k, v in items[:keep]}
+    if len(items) > keep:
+        out["other"] = round(sum(v for _k, v in items[keep:]) * 1e3)
+    return out
+
+
+def _end_to_end(engine, cfg, batch: int, context: int, steps: int, warmup: int, g) -> dict:
+    """``steps`` decode steps of ``batch`` requests at ``context`` through ``Engine.step``: the prompts go in as
+    host token ids, are prefilled in portions, and every timed step brings host token ids back."""
+    import torch
+
+    from stride_b200 import SamplingParams
+    prompts = [torch.randint(0, cfg.vocab_size, (context - 1,), generator=g).tolist() for _ in range(batch)]
+    # requests that finish their prompt early keep decoding while the others are still prefilled in portions
+    spare = batch * (-(-context // 2048)) + 16
+    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + spare, ignore_eos=True)
+    ids = [engine.add_request(p, params) for p in prompts]
+    while engine.scheduler.num_waiting or any(engine.scheduler.sequence(engine._seq_of_request[i]).state != engine._rt.SeqState.Decoding
+                                              for i in ids):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced, step_ms = 0, []
+    for _ in range(steps):
+        t_step = time.perf_counter()
+        produced += sum(1 for _rid, tok, _why in engine.step() if tok is not None)
+        step_ms.append((time.perf_counter() - t_step) * 1e3)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    if os.environ.get("STRIDE_BENCH_DEBUG"):
+        print("e2e step ms:", [round(x, 2) for x in step_ms], file=sys.stderr)
+        print("metrics:", engine.metrics(), file=sys.stderr)
+    if produced != batch * steps:
+        raise RuntimeError(f"the end-to-end loop produced {produced} tokens, expected {batch * steps}")
+    for i in ids:
+        engine.cancel(i)
+    while engine.step():        # a step launched ahead for the cancelled requests is dropped here
+        pass
+    return {"value": round(produced / elapsed, 1), "unit": "tokens/s", "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // steps,
+            "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // steps}
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -190,9 +242,14 @@ def run_ours(args) -> dict:
     cfg, full_layers = bench_config(args.layers, args.shape)
     batch, context, prompt_len = args.batch, args.context, 2048
     page = 16
-    need_tokens = max(64 * (context + 64), batch * (context + 1024)) + 4096
+    point_batches = sorted({int(b) for b in args.points.split(",") if b.strip()})
+    short_context = 2048 if context > 2048 else 0
+    # the pool holds the largest batch that is live at any one time (the points run one after the other), and the
+    # end-to-end requests, which decode past the context
+    most = max(point_batches + [batch])
+    need_tokens = max(most * (context + page), batch * (context + 1024), prompt_len) + 4096
     engine = Engine(config=cfg, random_weights=0, dtype="bfloat16", block_size=page, num_blocks=need_tokens // page + 64,
-                    max_batch_tokens=2048, max_batch_seqs=64, max_model_len=context + 1024, prefix_caching=False,
+                    max_batch_tokens=2048, max_batch_seqs=max(most, 8), max_model_len=context + 1024, prefix_caching=False,
                     check_invariants=False)
     for pages in engine.device_cache.pages:      # synthetic cache contents: small random keys and values
         pages.normal_(0.0, 0.5)
@@ -225,53 +282,40 @@ def run_ours(args) -> dict:
     # ---- decode points, device-timed graph replays on synthetic caches
     points, key_base = {}, 1000
     main = None
-    for b in (1, 64, batch):
-        sb, keys = _synthetic_decode_batch(engine, b, context, key_base)
+    runs = [(b, context) for b in point_batches if b != batch] + [(batch, context)]
+    if short_context:
+        runs = [(b, short_context) for b in sorted(set(point_batches + [batch]))] + runs
+    breakdown = {}
+    for b, c in runs:
+        sb, keys = _synthetic_decode_batch(engine, b, c, key_base)
         key_base += 1000
         ms, clocks, launches = _time_graph(engine, sb, args.steps, args.warmup)
+        if (b, c) == (batch, context):
+            main = (ms, clocks, launches)
+            if not args.no_breakdown:
+                engine.runner.timed_step(sb)                                    # once untimed: lazily loaded kernels
+                breakdown["decode"] = _rounded(engine.runner.timed_step(sb)[1])
+        else:
+            points[f"decode_b{b}" + ("" if c == context else f"_ctx{c}")] = round(b / ms * 1e3, 1)
         for k in keys:
             engine.cache.close(k)
-        if b == batch:
-            main = (ms, clocks, launches)
-        if b in (1, 64):
-            points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
     ms_per_step, clocks, launches = main
     value = batch / ms_per_step * 1e3
     achieved = decode_bytes(cfg, batch, context) / (ms_per_step * 1e-3) / 1e9
+    if not args.no_breakdown:
+        engine.cache.open(800000, "bench")
+        engine.cache.ensure(800000, prompt_len, 0)
+        sb = engine._rt.StepBatch(engine.cache)
+        sb.add(800000, prompt, 0, [prompt_len - 1])
+        breakdown["prefill"] = _rounded(engine.runner.timed_step(sb)[1])
+        engine.cache.close(800000)
 
     # ---- end to end through the entry point: real prompts, scheduling, sampling, host tokens in and out
     e2e = None
     if not args.no_e2e:
-        prompts = [torch.randint(0, cfg.vocab_size, (context - 1,), generator=g).tolist() for _ in range(batch)]
-        # requests that finish their prompt early keep decoding while the others are still prefilled in portions
-        spare = batch * (-(-context // 2048)) + 16
-        params = SamplingParams(temperature=0.0, max_tokens=max(args.warmup, 3) + args.steps + spare, ignore_eos=True)
-        ids = [engine.add_request(p, params) for p in prompts]
-        while engine.scheduler.num_waiting or any(engine.scheduler.sequence(engine._seq_of_request[i]).state != engine._rt.SeqState.Decoding
-                                                  for i in ids):
-            engine.step()
-        for _ in range(max(args.warmup, 3)):
-            engine.step()
-        h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        produced, step_ms = 0, []
-        for _ in range(args.steps):
-            t_step = time.perf_counter()
-            produced += sum(1 for _rid, tok, _why in engine.step() if tok is not None)
-            step_ms.append((time.perf_counter() - t_step) * 1e3)
-        torch.cuda.synchronize()
-        elapsed = time.perf_counter() - t0
-        if os.environ.get("STRIDE_BENCH_DEBUG"):
-            print("e2e step ms:", [round(x, 2) for x in step_ms], file=sys.stderr)
-            print("metrics:", engine.metrics(), file=sys.stderr)
-        if produced != batch * args.steps:
-            raise RuntimeError(f"the end-to-end loop produced {produced} tokens, expected {batch * args.steps}")
-        e2e = {"value": round(produced / elapsed, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // args.steps,
-               "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // args.steps}
-        for i in ids:
-            engine.cancel(i)
+        e2e = _end_to_end(engine, cfg, batch, context, args.steps, max(args.warmup, 3), g)
+        if batch != 1 and 1 in point_batches:
+            e2e["decode_b1"] = _end_to_end(engine, cfg, 1, context, args.steps, max(args.warmup, 3), g)["value"]
 
     return {
         "metric": f"{SHAPES[args.shape]} decode tok/s at batch {batch}, context {context} (bf16, one B200)",
@@ -288,7 +332,7 @@ def run_ours(args) -> dict:
         "e2e": e2e, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clocks, "gpu_launches": launches,
+        "points": points, "breakdown": breakdown, "clocks": clocks, "gpu_launches": launches,
     }
 
 
@@ -414,6 +458,8 @@ def main(argv=None) -> int:
                    help="layer sizes of another named model (the headline is the default)")
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (reported in config)")
     p.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    p.add_argument("--points", default="1,64", help="batch sizes of the extra decode points (comma-separated)")
+    p.add_argument("--no-breakdown", action="store_true", help="skip the per-class times of one decode step and the prefill")
     p.add_argument("--profile", choices=["decode", "prefill"], default=None,
                    help="run a few eager steps of one kind for a profiler instead of measuring")
     args = p.parse_args(argv)

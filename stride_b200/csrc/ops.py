@@ -67,7 +67,7 @@ _SIGNATURES = {
 }
 
 
-def _fn(name: str):
+def _fn(name: str, what: str | None = None):
     f = _bound.get(name)
     if f is None:
         library, argtypes = _SIGNATURES[name]
@@ -75,7 +75,67 @@ def _fn(name: str):
         f.argtypes = argtypes
         f.restype = c_int
         _bound[name] = f
+    if _timer is not None:
+        return _timer.timed(what or _CLASS_OF.get(name, name), f)
     return f
+
+
+# ---------------------------------------------------------------- time per class of kernel
+# What a launcher counts as when the time of a step is split up. Matrix products say more (their shape) at the call.
+_CLASS_OF = {
+    "stride_embed_gather": "embedding", "stride_add_rmsnorm": "norm", "stride_add_residual": "residual sum",
+    "stride_scale_rows": "norm", "stride_zero_fresh_state": "state slots", "stride_rope_kv_write": "rotation + cache write",
+    "stride_silu_mul": "silu * up", "stride_paged_attention_generic": "attention (exact kernel)",
+    "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
+    "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling",
+}
+
+
+class KernelTimer:
+    """Device time per class of kernel inside a step, from CUDA events around every launch (the reference records
+    one duration per pass, python/stride_worker/model.py:238-240,343-345; this splits it up). Use::
+
+        with ops.KernelTimer() as timer:
+            model.forward(ctx)              # eagerly: a captured graph has no place for events
+        timer.milliseconds()                # {"attention (decode)": 1.52, "product 6144x4096 (qkv + rotation)": 1.18, ...}
+
+    The events stand between the kernels, so launches do not overlap their predecessors' tails as they do in a
+    real step: the classes' shares are right, their sum is somewhat above the step's own time."""
+
+    def __init__(self):
+        self.spans: list = []       # (class, start event, end event)
+
+    def __enter__(self):
+        global _timer
+        if _timer is not None:
+            raise KernelError("a KernelTimer is active already")
+        _timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+
+    def timed(self, what: str, call):
+        def run(*args):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = call(*args)
+            end.record()
+            self.spans.append((what, start, end))
+            return code
+        return run
+
+    def milliseconds(self) -> dict:
+        """Synchronises; class -> summed device time, largest first."""
+        torch.cuda.synchronize()
+        out: dict = {}
+        for what, start, end in self.spans:
+            out[what] = out.get(what, 0.0) + start.elapsed_time(end)
+        return dict(sorted(out.items(), key=lambda kv: -kv[1]))
+
+
+_timer: KernelTimer | None = None
 
 
 # How many of the package's own kernels were launched (library matrix products
@@ -298,7 +358,7 @@ def linear_tc(x, weight, out) -> bool:
     n = weight.shape[0]
     st = _tc_buffers(x.device, _tc_scratch_floats(n, m, k))
     partials = st["partials"]
-    code = _fn("stride_gemm_tc_skinny")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
+    code = _fn("stride_gemm_tc_skinny", f"product {n}x{k} (tcgen05)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
                                         m, n, k, int(out.dtype == torch.float32),
                                         None if partials is None else partials.data_ptr(),
                                         0 if partials is None else partials.numel(), st["tickets"].data_ptr(), _TC_TICKETS,
@@ -351,7 +411,7 @@ def linear_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
     if not (FOLD_NORMS and STREAM_GEMM) or m > TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16 or residual.shape != (m, n):
         return 0
     count = c_int(0)
-    code = _fn("stride_gemm_stream_add_norm")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
+    code = _fn("stride_gemm_stream_add_norm", f"product {n}x{k} (+ residual, norm statistics)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
                                               _dev(xt, "xt", torch.bfloat16), _dev(residual, "residual", torch.float32),
                                               _dev(norm_weight, "norm_weight", torch.float32), _dev(partials, "partials", torch.float32),
                                               partials.numel(), m, n, k, ctypes.byref(count), _status_ptr(x.device), _stream())
@@ -372,7 +432,7 @@ def linear_gated_tc(x, weight, out, folded=None) -> bool:
         return False
     st = _tc_buffers(x.device, 0)
     partials, count, eps = _fold_args(folded)
-    code = _fn("stride_gemm_tc_gated")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
+    code = _fn("stride_gemm_tc_gated", f"product 2x{inter}x{k} (tcgen05, silu * up)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16),
                                        _dev(out, "out", torch.bfloat16), m, inter, k, st["status"].data_ptr(), partials, count, eps,
                                        _stream())
     if code == -2:
@@ -390,7 +450,7 @@ def linear_stream(x, weight, out) -> bool:
     Returns False when the kernel does not take the shape."""
     m, k = x.shape
     n = weight.shape[0]
-    code = _fn("stride_gemm_stream_bf16")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
+    code = _fn("stride_gemm_stream_bf16", f"product {n}x{k} (weight streaming)")(_dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"),
                                           m, n, k, int(out.dtype == torch.float32), _status_ptr(x.device), _stream())
     if code == -2:
         return False
@@ -409,7 +469,7 @@ def linear_qkv_rope(x, weight, qkv, bias, positions, slot_mapping, cos, sin, k_p
     if not STREAM_GEMM or m > TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16 or qkv.shape != (m, (nq + 2 * nkv) * hd):
         return False
     partials, count, eps = _fold_args(folded)
-    code = _fn("stride_gemm_stream_qkv_rope")(
+    code = _fn("stride_gemm_stream_qkv_rope", f"product {weight.shape[0]}x{k} (qkv + rotation + cache write)")(
         _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(qkv, "qkv", torch.bfloat16),
         _opt(bias, "bias", torch.float32), _dev(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
         _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages", torch.bfloat16),
@@ -437,7 +497,7 @@ def linear(x, weight, out) -> None:
     if weight.shape[1] != k or out.shape != (m, n):
         raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> {tuple(out.shape)} do not agree")
     if x.dtype == torch.float32:
-        _check(_fn("stride_gemm_nt_f32")(_dev(x, "x", torch.float32), _dev(weight, "weight", torch.float32),
+        _check(_fn("stride_gemm_nt_f32", f"product {n}x{k} (float32)")(_dev(x, "x", torch.float32), _dev(weight, "weight", torch.float32),
                                          _dev(out, "out", torch.float32), m, n, k, k, k, n, _stream()), "gemm_nt_f32")
         return
     _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out")
@@ -451,10 +511,13 @@ def linear(x, weight, out) -> None:
                 return
         elif STREAM_GEMM and linear_stream(x, weight, out):
             return
-    if out.dtype == torch.float32:
-        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
-    else:
-        torch.mm(x, weight.t(), out=out)
+    def library(*_):
+        if out.dtype == torch.float32:
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        else:
+            torch.mm(x, weight.t(), out=out)
+        return 0
+    (_timer.timed(f"product {n}x{k} (library)", library) if _timer is not None else library)()
 
 
 # -------------------------------------------------------------------- attention

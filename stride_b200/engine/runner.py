@@ -112,6 +112,16 @@ class ModelRunner:
             return logits.cpu() if to_host else logits
         return self._step_eager(batch, to_host)
 
+    def timed_step(self, batch):
+        """The same step run eagerly with CUDA events around every launch: ``(logits, {class of kernel:
+        milliseconds})``. For looking at where a step's time goes; a step that generation runs is not timed."""
+        self._token_source = None
+        if batch.num_tokens > self.token_capacity or batch.num_seqs > self.seq_capacity or batch.max_ctx > self.max_model_len:
+            raise ValueError("the step does not fit the runner")
+        with ops.KernelTimer() as timer:
+            logits = self._step_eager(batch, to_host=False)
+        return logits, timer.milliseconds()
+
     # ------------------------------------------------------------------- eager
     def _context(self, staging, batch, num_tokens, num_rows, for_graph: int = 0):
         items, row = [], 0
