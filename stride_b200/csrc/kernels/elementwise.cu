@@ -260,6 +260,61 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     }
 }
 
+// The same arithmetic once more in the form that streams fastest: one pack of V consecutive columns per thread
+// (8 for bfloat16, 4 for float32; hidden <= V * blockDim.x), every load issued before anything is computed or
+// stored, so that a store to the residual never stands between two loads. One CTA per row.
+template <typename T>
+__global__ void add_rmsnorm_pack_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                        const float* __restrict__ weight, T* __restrict__ out,
+                                        const int32_t* __restrict__ rows, int hidden, float eps) {
+    pdl_trigger();
+    constexpr int V = Pack<T>::V;
+    __shared__ float scratch[32];
+    const int c = threadIdx.x * V;
+    const bool live = c < hidden;
+    // the norm's weight does not depend on the kernel before this one: fetch it while that one finishes
+    float w[V];
+#pragma unroll
+    for (int j = 0; j < V; j += 4) {
+        const float4 t = live ? *reinterpret_cast<const float4*>(weight + c + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        w[j] = t.x; w[j + 1] = t.y; w[j + 2] = t.z; w[j + 3] = t.w;
+    }
+    pdl_wait();
+    const int r = blockIdx.x;
+    const size_t s = rows ? static_cast<size_t>(rows[r]) : static_cast<size_t>(r);
+    float* res = residual + s * hidden;
+    float x[V];
+    Pack<T> d;
+    if (live) {
+#pragma unroll
+        for (int j = 0; j < V; j += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(res + c + j);
+            x[j] = t.x; x[j + 1] = t.y; x[j + 2] = t.z; x[j + 3] = t.w;
+        }
+        if (delta) d.load(delta + s * hidden + c);
+    }
+    float sq = 0.f;
+    if (live) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            if (delta) x[j] = __fadd_rn(x[j], d.v[j]);
+            sq = fmaf(x[j], x[j], sq);
+        }
+        if (delta && !rows) {
+#pragma unroll
+            for (int j = 0; j < V; j += 4) *reinterpret_cast<float4*>(res + c + j) = make_float4(x[j], x[j + 1], x[j + 2], x[j + 3]);
+        }
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    if (live) {
+        Pack<T> y;
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.v[j] = __fmul_rn(__fmul_rn(x[j], inv), w[j]);
+        y.store(out + static_cast<size_t>(r) * hidden + c);
+    }
+}
+
 // rope_kv_write_kernel with 16-byte accesses: one unit of work is V consecutive
 // pair indices of one head (needs hd / 2 to be a multiple of V).
 template <typename T>
@@ -315,6 +370,70 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
             a.store(dst + i);
             b.store(dst + i + half);
         }
+    }
+}
+
+// The same with one unit of work per thread and no loop (a unit: V consecutive pair indices of one head, i.e. one
+// pack from each half of the head), loads before stores: blockIdx.x is the token, blockIdx.y a chunk of the units.
+template <typename T>
+__global__ void rope_kv_write_pack_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                                          const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
+                                          const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                          T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd,
+                                          int page_size, int rotate) {
+    pdl_trigger();
+    constexpr int V = Pack<T>::V;
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int per_head = half / V;
+    const int heads = nq + 2 * nkv;
+    const int w = blockIdx.y * blockDim.x + threadIdx.x;
+    if (w >= heads * per_head) return;
+    const int head = w / per_head, i = (w - head * per_head) * V;
+    const int pos = positions[t];                  // the step's index arrays are not written by the kernel before
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    const bool turns = head < nq + nkv && rotate;
+    float c[V], sn[V];
+    if (turns) {
+#pragma unroll
+        for (int j = 0; j < V; j += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(cos_table + static_cast<size_t>(pos) * half + i + j);
+            const float4 b = *reinterpret_cast<const float4*>(sin_table + static_cast<size_t>(pos) * half + i + j);
+            c[j] = a.x; c[j + 1] = a.y; c[j + 2] = a.z; c[j + 3] = a.w;
+            sn[j] = b.x; sn[j + 1] = b.y; sn[j + 2] = b.z; sn[j + 3] = b.w;
+        }
+    }
+    pdl_wait();
+    T* x = qkv + (static_cast<size_t>(t) * heads + head) * hd;
+    Pack<T> a, b;
+    a.load(x + i);
+    b.load(x + i + half);
+    if (bias) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            a.v[j] = __fadd_rn(a.v[j], bias[head * hd + i + j]);
+            b.v[j] = __fadd_rn(b.v[j], bias[head * hd + i + half + j]);
+        }
+    }
+    if (turns) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const float ra = __fadd_rn(__fmul_rn(a.v[j], c[j]), __fmul_rn(-b.v[j], sn[j]));
+            const float rb = __fadd_rn(__fmul_rn(b.v[j], c[j]), __fmul_rn(a.v[j], sn[j]));
+            a.v[j] = ra;
+            b.v[j] = rb;
+        }
+    }
+    if (head < nq) {
+        a.store(x + i);
+        b.store(x + i + half);
+    } else if (slot >= 0) {
+        const int page = slot / page_size, offset = slot % page_size;
+        const bool is_key = head < nq + nkv;
+        const int kvh = is_key ? head - nq : head - nq - nkv;
+        T* dst = (is_key ? k_pages : v_pages) + ((static_cast<size_t>(page) * nkv + kvh) * page_size + offset) * hd;
+        a.store(dst + i);
+        b.store(dst + i + half);
     }
 }
 
@@ -447,6 +566,17 @@ int stride_add_rmsnorm(float* residual, const void* delta, const float* weight, 
         const uintptr_t bits = reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
                                reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out);
         const int quads = hidden / 4;
+        // one pack per thread where a row fits one CTA that way (the choice depends on the width alone, never on the
+        // number of rows, so a row's bits do not depend on what else is in the batch)
+        const int pack = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
+        if (hidden % pack == 0 && bits % 16 == 0 && hidden / pack <= 1024 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
+            const int pthreads = (hidden / pack + 31) / 32 * 32;
+            if (dtype == STRIDE_DTYPE_F32)
+                stride::launch(add_rmsnorm_pack_kernel<float>, dim3(num_rows), dim3(pthreads), 0, stream, residual, static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
+            else
+                stride::launch(add_rmsnorm_pack_kernel<__nv_bfloat16>, dim3(num_rows), dim3(pthreads), 0, stream, residual, static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
+            return STRIDE_LAUNCH_STATUS();
+        }
         if (hidden % 4 == 0 && bits % 16 == 0 && quads <= 8 * 256 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
             const int threads = quads <= 32 ? 32 : (quads <= 64 ? 64 : (quads <= 128 ? 128 : 256));
             const int iters = (quads + threads - 1) / threads;
@@ -522,6 +652,16 @@ int stride_rope_kv_write(void* qkv, const float* bias, const int32_t* positions,
         const int vec = dtype == STRIDE_DTYPE_F32 ? 4 : 8;
         if (bits % 16 == 0 && (hd / 2) % vec == 0 && (dtype == STRIDE_DTYPE_F32 || dtype == STRIDE_DTYPE_BF16)) {
             const int units = work / vec;
+            if (reinterpret_cast<uintptr_t>(cos_table) % 16 == 0 && reinterpret_cast<uintptr_t>(sin_table) % 16 == 0 && (hd / 2) % 4 == 0) {
+                // one unit per thread, no loop
+                const int pthreads = units >= 512 ? 256 : (units + 31) / 32 * 32;
+                const dim3 grid(tokens, (units + pthreads - 1) / pthreads);
+                if (dtype == STRIDE_DTYPE_F32)
+                    stride::launch(rope_kv_write_pack_kernel<float>, grid, dim3(pthreads), 0, stream, static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
+                else
+                    stride::launch(rope_kv_write_pack_kernel<__nv_bfloat16>, grid, dim3(pthreads), 0, stream, static_cast<__nv_bfloat16*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), nq, nkv, hd, page_size, rotate);
+                return STRIDE_LAUNCH_STATUS();
+            }
             const int vthreads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
             if (dtype == STRIDE_DTYPE_F32)
                 stride::launch(rope_kv_write_vec_kernel<float>, dim3(tokens), dim3(vthreads), 0, stream, static_cast<float*>(qkv), bias, positions, slot_mapping, cos_table, sin_table, static_cast<float*>(k_pages), static_cast<float*>(v_pages), nq, nkv, hd, page_size, rotate);
