@@ -293,7 +293,13 @@ def test_seeded_sampling(case, dtype):
     assert a == b and a != c and all(0 <= t < case["cfg"]["vocab_size"] for t in a + c)
     greedy_tokens = run(temperature=0.0)
     assert run(temperature=1.0, top_k=1, seed=3) == greedy_tokens
-    assert run(temperature=1e-4, seed=4) == greedy_tokens, "a vanishing temperature must pick the maximum"
+    cold = run(temperature=1e-4, seed=4)
+    if dtype == "float32":
+        assert cold == greedy_tokens, "a vanishing temperature must pick the maximum"
+    else:
+        # two logits that bfloat16 cannot tell apart may fall either way: every token must be a maximum of the plain
+        # logits within rounding, and the run may part from the greedy one only at such a near-tie
+        assert_greedy(case, dtype, prompt, cold, "a vanishing temperature must pick the maximum")
     ranked = run(temperature=1.0, top_k=2, top_p=0.9, seed=5)
     assert ranked == run(temperature=1.0, top_k=2, top_p=0.9, seed=5) and len(ranked) == 16
     # the host-ranked path draws from the two most likely tokens only
