@@ -17,6 +17,14 @@
 // last ticket adds the partials in split order and stores the result. Nobody
 // waits for another CTA.
 //
+// For 17 to 64 tokens (decode steps of many requests) the CTAs that share an output
+// tile form a thread-block cluster instead (CLUSTER): when all of them have finished
+// their part of K, the others write their accumulators into the first one's shared
+// memory (the ring, no longer in use) over the cluster's network, and the first adds
+// them in split order and stores the tile. No partial tile touches global memory;
+// the cluster's barrier, which every CTA of it passes twice, is the only wait, and
+// CTAs of a cluster are guaranteed to run together.
+//
 // Every wait on an mbarrier is bounded by a clock; a wait that runs out sets
 // *status and the CTA winds down (tensor memory is freed on every path).
 #include <cstdio>
@@ -48,7 +56,7 @@ __device__ __forceinline__ void store_value<__nv_bfloat16>(__nv_bfloat16* p, flo
 // GATED (swapped use, one split, bfloat16 out): the rows of A alternate in blocks of 64 between the gate and the
 // up matrix of a gated feed-forward; the tile's rows 0-63 and 64-127 then belong together, and the epilogue writes
 // silu(gate) * up, 64 columns of the inner activation per tile, instead of the 128 products.
-template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename OutT, bool GATED = false>
+template <int BLOCK_N, int STAGES, bool TRANSPOSED, bool A_INDEPENDENT, typename OutT, bool GATED = false, bool CLUSTER = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out,
                     int ldo, int M, int N, int K, int k_blocks_per_split, float* __restrict__ partials,
@@ -112,6 +120,12 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tma_load_2d(a_dst + A_BYTES, &map_b, bar, (kb_begin + i) * kBlockK, n0);
             }
         }
+        __syncwarp();
+        if constexpr (CLUSTER) {       // take part in the cluster's two barriers (see the epilogue)
+            cluster_arrive();
+            cluster_wait();
+            cluster_arrive();
+        }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- tensor-core issuer
@@ -133,6 +147,12 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             umma_commit(smem_u32(&done_bar));              // the accumulator is complete
         }
+        __syncwarp();
+        if constexpr (CLUSTER) {
+            cluster_arrive();
+            cluster_wait();
+            cluster_arrive();
+        }
     } else {
         // ---- epilogue: warps 2..5 own the lane quadrants 2, 3, 0, 1 of tensor memory
         const int quad = warp & 3;
@@ -147,6 +167,71 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool ok = mbar_wait(smem_u32(&done_bar), 0, status, 3);
         tc_fence_after();
         pdl_wait();        // returns at once here (the producer passed it long ago); keeps this thread's stores ordered too
+        if constexpr (CLUSTER) {
+            // The CTAs of the cluster hold the same output tile for different parts of K (blockIdx.z = rank in the
+            // cluster). First barrier: every CTA's products are complete, so every ring is free and every CTA runs.
+            // Then the others send their accumulators into the first CTA's ring, [rank - 1][row][BLOCK_N] float32 with
+            // the 16-byte chunks of a row permuted by the row's low bits (a thread owns a row: without that all lanes
+            // of a warp would hit one bank). Second barrier: the partial tiles have landed; the first CTA adds them in
+            // the order of the ranks and stores.
+            static_assert(!CLUSTER || !GATED, "the gated epilogue is not written for clusters");
+            constexpr int CHUNKS = BLOCK_N / 4, MASK = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+            const uint32_t rank = cluster_rank();
+            float* part = reinterpret_cast<float*>(smem);
+            cluster_arrive();
+            cluster_wait();
+            if (rank != 0) {
+#pragma unroll
+                for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
+                    float v[16];
+                    if (ok && num_kb > 0) {
+                        tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j += 4) {
+                        const int chunk = ((c0 + j) / 4) ^ (row & MASK);
+                        store_cluster_f4(smem_u32(part + (static_cast<size_t>(rank - 1) * kBlockM + row) * BLOCK_N + chunk * 4), 0, v[j], v[j + 1],
+                                         v[j + 2], v[j + 3]);
+                    }
+                }
+                cluster_arrive();
+            } else {
+                cluster_arrive();
+                cluster_wait();
+                const int r = m0 + row;
+#pragma unroll
+                for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
+                    float v[16];
+                    if (ok && num_kb > 0) {
+                        tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + c0, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+                    for (int z = 1; z < static_cast<int>(gridDim.z); ++z) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const int chunk = ((c0 + j) / 4) ^ (row & MASK);
+                            const float4 p = *reinterpret_cast<const float4*>(part + (static_cast<size_t>(z - 1) * kBlockM + row) * BLOCK_N + chunk * 4);
+                            v[j] += p.x; v[j + 1] += p.y; v[j + 2] += p.z; v[j + 3] += p.w;
+                        }
+                    }
+                    if (ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int c = n0 + c0 + j;
+                            if (r < M && c < N) {
+                                if (TRANSPOSED) store_value<OutT>(out + static_cast<size_t>(c) * ldo + r, v[j]);
+                                else store_value<OutT>(out + static_cast<size_t>(r) * ldo + c, v[j]);
+                            }
+                        }
+                    }
+                }
+            }
+        } else {
         const bool split = gridDim.z > 1;
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         float* my_partial = split ? partials + ((static_cast<size_t>(blockIdx.z) * gridDim.x * gridDim.y + tile) * kBlockM + row) * BLOCK_N
@@ -257,6 +342,7 @@ gemm_tn_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (threadIdx.x == 64) tickets[tile] = 0;            // ready for the next launch
             }
         }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -283,12 +369,76 @@ int launch(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ld
     return STRIDE_LAUNCH_STATUS();
 }
 
+// The product with the CTAs of an output tile in a cluster of `splits` (1 to 8): no scratch in global memory.
+template <int BLOCK_N, int STAGES, typename OutT>
+int launch_clustered(const CUtensorMap* map_a, const CUtensorMap* map_b, OutT* out, int ldo, int M, int N, int K, int splits,
+                     int* status, cudaStream_t stream) {
+    constexpr int smem = STAGES * (kBlockM * kBlockK * 2 + BLOCK_N * kBlockK * 2) + 1024;
+    static bool configured[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return STRIDE_BAD_ARGUMENT;
+    auto kernel = gemm_tn_bf16_kernel<BLOCK_N, STAGES, true, true, OutT, false, true>;
+    if (!configured[device]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured[device] = true;
+    }
+    // the partial tiles of the other CTAs must fit the first one's ring
+    if (static_cast<long long>(splits - 1) * kBlockM * BLOCK_N * 4 > smem - 1024) return STRIDE_UNSUPPORTED;
+    const int k_blocks = (K + kBlockK - 1) / kBlockK;
+    const int per_split = (k_blocks + splits - 1) / splits;
+    dim3 grid((M + kBlockM - 1) / kBlockM, (N + BLOCK_N - 1) / BLOCK_N, splits);
+    stride::launch_clusters(kernel, grid, dim3(kThreads), smem, stream, splits, *map_a, *map_b, out, ldo, M, N, K, per_split,
+                            static_cast<float*>(nullptr), static_cast<int*>(nullptr), status, static_cast<const float*>(nullptr), 0, 0.f);
+    return STRIDE_LAUNCH_STATUS();
+}
+
 }  // namespace tc
 }  // namespace stride
 
 using namespace stride;
 
 extern "C" {
+
+// CTAs per output tile for the clustered product: as many as it takes to put a CTA on every SM, each with at least
+// four 64-wide blocks of K, at most four (what the ring holds of partial tiles at 64 tokens).
+int stride_gemm_tc_cluster_splits(int rows_a, int k) {
+    const int tiles = (rows_a + tc::kBlockM - 1) / tc::kBlockM;
+    const int k_blocks = (k + tc::kBlockK - 1) / tc::kBlockK;
+    int splits = 148 / (tiles > 0 ? tiles : 1);
+    if (splits > 4) splits = 4;
+    if (splits > k_blocks / 4) splits = k_blocks / 4;
+    return splits < 1 ? 1 : splits;
+}
+
+// out = x @ w^T for 17 to 64 tokens (it takes fewer too), computed swapped with the CTAs of an output tile in a
+// cluster; see the kernel. Needs no scratch. Returns -2 for shapes it does not take (k % 8 != 0, more than 64
+// tokens, unaligned pointers); the caller then uses the library product.
+int stride_gemm_tc_clustered(const void* x, const void* w, void* out, int tokens, int n_out, int k, int out_is_f32, int* status,
+                             cudaStream_t stream) {
+    if (tokens < 0 || n_out <= 0 || k <= 0) return STRIDE_BAD_ARGUMENT;
+    if (tokens == 0) return 0;
+    if (tokens > 64 || k % 8 || (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16) return STRIDE_UNSUPPORTED;
+    if (status == nullptr) return STRIDE_BAD_ARGUMENT;
+    const int block_n = tokens <= 16 ? 16 : (tokens <= 32 ? 32 : 64);
+    const int splits = stride_gemm_tc_cluster_splits(n_out, k);
+    const CUtensorMap* map_a = tc::cached_map(w, n_out, k, k, tc::kBlockM);
+    const CUtensorMap* map_b = tc::cached_map(x, tokens, k, k, block_n);
+    if (!map_a || !map_b) return STRIDE_UNSUPPORTED;
+#define STRIDE_TC_CLUSTERED(BN, ST)                                                                                              \
+    (out_is_f32 ? tc::launch_clustered<BN, ST, float>(map_a, map_b, static_cast<float*>(out), n_out, n_out, tokens, k, splits,   \
+                                                      status, stream)                                                           \
+                : tc::launch_clustered<BN, ST, __nv_bfloat16>(map_a, map_b, static_cast<__nv_bfloat16*>(out), n_out, n_out,      \
+                                                              tokens, k, splits, status, stream))
+    switch (block_n) {
+        // stages sized so that two CTAs fit one SM (a ring as deep as shared memory allows, one CTA per SM, measured
+        // 7 % slower over a decode step of 32 tokens: the widest matrix has 224 tiles for 148 SMs)
+        case 16: return STRIDE_TC_CLUSTERED(16, 6);
+        case 32: return STRIDE_TC_CLUSTERED(32, 5);
+        default: return STRIDE_TC_CLUSTERED(64, 4);
+    }
+#undef STRIDE_TC_CLUSTERED
+}
 
 // How many CTAs split the K range for these sizes (also sizes the scratch): enough
 // to give every SM about two CTAs, each with at least eight 64-wide K blocks.

@@ -43,6 +43,7 @@ _SIGNATURES = {
                                                              c_int, c_int, c_void_p]),
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
+    "stride_gemm_tc_clustered": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_qkv_rope": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -369,6 +370,29 @@ def linear_tc(x, weight, out) -> bool:
     return True
 
 
+# The tcgen05 kernel with the CTAs of an output tile in a cluster (the parts of K meet in the first CTA's shared
+# memory, nothing goes through global memory) takes up to 64 tokens. Measured over whole decode steps of the 8B shape
+# at a context of 2,048 it is level with the library product at 17 and 32 tokens (4.51 against 4.44 ms, 5.11 against
+# 5.02) and slower at 64 (7.3 against 6.3: there the library streams the small matrices in 48- and 64-row tiles
+# through a 15-stage ring at about 0.6 of the memory bandwidth, this kernel's 128-row tiles with K split four ways at
+# 0.35), so it is off by default: STRIDE_TC_CLUSTER_MAX_TOKENS=64 switches it on.
+TC_CLUSTER_MAX_TOKENS = int(_os.environ.get("STRIDE_TC_CLUSTER_MAX_TOKENS", "0"))
+
+
+def linear_tc_clustered(x, weight, out) -> bool:
+    """``out = x @ weight.T`` for up to 64 rows of ``x`` on the clustered tcgen05 kernel. Returns False when the
+    kernel does not take the shape."""
+    m, k = x.shape
+    n = weight.shape[0]
+    code = _fn("stride_gemm_tc_clustered", f"product {n}x{k} (tcgen05, clusters)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"), m, n, k,
+        int(out.dtype == torch.float32), _status_ptr(x.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_tc_clustered")
+    return True
+
+
 GATED_BLOCK = 64      # rows of gate and up alternate in blocks of this many in a weight laid out for ``linear_gated_tc``
 
 
@@ -511,6 +535,8 @@ def linear(x, weight, out) -> None:
                 return
         elif STREAM_GEMM and linear_stream(x, weight, out):
             return
+    elif m <= TC_CLUSTER_MAX_TOKENS and TC_GEMM_MAX_TOKENS > 0 and linear_tc_clustered(x, weight, out):
+        return
     def library(*_):
         if out.dtype == torch.float32:
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)

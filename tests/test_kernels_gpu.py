@@ -410,6 +410,27 @@ def test_decode_attention_split_over_the_keys(ops, nq, nkv, hd, page, window):
     assert not ops.fast_attention_supported(torch.float32, 4, 2, 128)
 
 
+@pytest.mark.parametrize("tokens,n,k", [(17, 4096, 4096), (33, 6144, 4096), (64, 4096, 14336), (64, 28672, 4096), (40, 1000, 520),
+                                        (64, 384, 256), (20, 128256, 1024), (5, 4096, 2048)])
+def test_the_clustered_product_for_17_to_64_tokens(ops, tokens, n, k):
+    """The tcgen05 product whose CTAs of an output tile form a cluster and add their parts of K through shared
+    memory: matrices of one to a thousand 128-row tiles, K split over one to four CTAs, rows and widths that fill no
+    whole tile, float32 and bfloat16 results; twice in a row on other data (nothing is left behind)."""
+    g = torch.Generator().manual_seed(tokens + n)
+    for turn in range(2):
+        x = (torch.randn(tokens, k, generator=g) * 0.5).bfloat16()
+        w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+        w[min(n - 1, 130), :] = w[min(n - 1, 130), :] * 8       # one row stands out: a tile or a split that is dropped shows
+        want = x.double() @ w.double().T
+        scale = float(want.abs().max())
+        for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):       # as for the product of few tokens
+            out = torch.full((tokens, n), 7.0, dtype=out_dtype, device="cuda")
+            assert ops.linear_tc_clustered(dev(x), dev(w), out), "the kernel refused the shape"
+            ops.check_kernel_status()
+            err = float((out.double().cpu() - want).abs().max())
+            assert err <= tol * scale, f"{out_dtype}: max abs error {err:.3e} against scale {scale:.3e}"
+
+
 def test_decode_attention_refuses_a_position_beyond_the_bound_of_its_launch(ops):
     """A launch is sized for positions below ``max_context``. A row beyond it would wait for splits that were never
     launched; it gets zeros and a code in the status word instead, and leaves no ticket behind: the next launch on
