@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from ..weights import load_weights
+from ..weights import check_source, load_weights
 from .base import build_part
 from .runtime import ResidualStream, Runtime
 
@@ -48,12 +48,17 @@ class DecoderModel:
     def load(self, source) -> None:
         """Reads every declared tensor from ``source`` (checked first; one error
         lists all that is missing, unexpected or mis-shaped) and hands them out."""
-        weights = load_weights(source, self.declare(), self.rt.dtype, self.rt.device, self.spec.ignorable_tensors)
-        self.embedding.bind(weights)
-        for layer in self.layers:
-            layer.bind(weights)
-        self.final_norm.bind(weights)
-        self.head.bind(weights, tied=self.embedding.table())
+        check_source(source, self.declare(), self.spec.ignorable_tensors)
+        # Part by part: a part that fuses tensors at load (q/k/v into one matrix, gate and up interleaved) holds its
+        # own copy, so the tensors as stored are dropped as soon as the part has bound them. Loaded all at once, a
+        # model whose weights fill most of the device would need them twice.
+        for part in self._parts():
+            weights = load_weights(source, part.declare(), self.rt.dtype, self.rt.device, checked=True)
+            if part is self.head:
+                part.bind(weights, tied=self.embedding.table())
+            else:
+                part.bind(weights)
+            del weights
 
     def named_tensors(self) -> dict:
         d = {}

@@ -81,10 +81,13 @@ def check_source(source: WeightSource, declared: dict, ignorable: tuple = ()) ->
         raise WeightMismatchError(missing, unexpected, wrong_shape, wrong_kind)
 
 
-def load_weights(source: WeightSource, declared: dict, compute_dtype: torch.dtype, device, ignorable: tuple = ()) -> dict:
-    """Checks the source against the declarations, then moves every declared
-    tensor to ``device`` in its target dtype. Returns name -> tensor."""
-    check_source(source, declared, ignorable)
+def load_weights(source: WeightSource, declared: dict, compute_dtype: torch.dtype, device, ignorable: tuple = (),
+                 checked: bool = False) -> dict:
+    """Checks the source against the declarations (unless the caller has checked the whole model already and
+    now loads it part by part), then moves every declared tensor to ``device`` in its target dtype. Returns
+    name -> tensor."""
+    if not checked:
+        check_source(source, declared, ignorable)
     have = set(source.names())
     out = {}
     for name, decl in declared.items():
