@@ -233,6 +233,14 @@ def test_a_long_prompt_alone_is_prefilled_in_full_portions_from_a_graph(case, dt
     engine = engine_for(case, dtype, max_batch_tokens=16, max_batch_seqs=4)
     out = engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
     assert_greedy(case, dtype, prompt, out.tokens, "full portions from a graph")
+    if case["name"] == "D":
+        # portions of 48 tokens: above 16 rows the bfloat16 products are the library's and the prefill attention on
+        # tcgen05 runs, from the captured graph, at positions 48 and 96
+        wide = engine_for(case, dtype, max_batch_tokens=48, max_batch_seqs=4)
+        long_prompt = seeded_tokens(3 * 48 + 7, case["cfg"]["vocab_size"], 778)
+        more = wide.generate([long_prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
+        assert_greedy(case, dtype, long_prompt, more.tokens, "portions of 48 from a graph")
+        assert ("portion", 0) in wide.runner._graphs and wide.runner.graph_replays >= 3
     assert ("portion", 0) in engine.runner._graphs, "no full portion went through the graph"
     replays = engine.runner.graph_replays
     again = engine.generate([prompt[:40] + prompt[:13]], SamplingParams(temperature=0.0, max_tokens=6))[0]       # other positions, same graph

@@ -147,6 +147,25 @@ def test_decoding_across_context_buckets(case, monkeypatch):
     assert len({k[1] for k in session.runner._graphs if k[0] != "portion"}) >= 3, "the context never moved to another graph"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("live", [20, 33, 64])
+def test_many_requests_decoding_together(case, dtype, live):
+    """Up to 64 requests live at once, all decoding in the same steps: the decode graphs for 32 and 64 rows, where
+    the bfloat16 products go to the library and norm, rotation and SiLU run as kernels of their own."""
+    from stride_b200.engine.trace import TraceSession
+    vocab = case["cfg"]["vocab_size"]
+    requests = {f"r{i}": seeded_tokens(9 + (i * 7) % 41, vocab, 3000 + i) for i in range(live)}
+    _, state = read_model_dir(case["dirs"][dtype])
+    want = {rid: plain.forward(case["cfg"], state, t, torch.float64) for rid, t in requests.items()}
+    steps = modes.decoding_together(requests, decode_steps=8)
+    session = TraceSession(case["dirs"][dtype], dtype, max_tokens=modes.peak_tokens(steps), block_size=case["page"], max_requests=live)
+    got = replay(session, steps)
+    assert len(got) == live * 9
+    check(got, want, dtype, f"{live} requests decoding together")
+    assert session.runner.graph_replays >= 7, "the decode steps did not go through captured graphs"
+    assert max(session.runner.captured_buckets()) >= min(live, 64)
+
+
 def test_an_unknown_token_or_too_few_pages_is_an_error_not_a_wrong_result(case):
     from stride_b200.engine.trace import TraceError, TraceSession
     s = TraceSession(case["dirs"]["float32"], "float32", max_tokens=64, block_size=case["page"])
