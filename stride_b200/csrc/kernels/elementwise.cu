@@ -490,18 +490,18 @@ __global__ void embed_gather_vec_kernel(const int32_t* __restrict__ ids, const i
 }
 
 // The second half of an RMS norm that was folded into the product before it (gemm_bf16_stream.cu, RowNorm): x~
-// holds residual * weight in bfloat16, `partials` [count][16] the sums of squares of the residual per producer CTA
+// holds residual * weight in bfloat16, `partials` [count][token_stride] the sums of squares of the residual per producer CTA
 // and token. out = x~ * rsqrt(sum / width + eps). Only needed when what consumes the norm cannot apply the factor
 // itself.
 __global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ xt, const float* __restrict__ partials, int count, float eps,
-                                  __nv_bfloat16* __restrict__ out, int width) {
+                                  __nv_bfloat16* __restrict__ out, int width, int token_stride) {
     pdl_trigger();
     pdl_wait();
     __shared__ float factor;
     const int t = blockIdx.x;
     if (threadIdx.x == 0) {
         float total = 0.f;
-        for (int c = 0; c < count; ++c) total += partials[c * 16 + t];
+        for (int c = 0; c < count; ++c) total += partials[c * token_stride + t];
         factor = rsqrtf(total / static_cast<float>(width) + eps);
     }
     __syncthreads();
@@ -708,11 +708,11 @@ int stride_silu_mul(const void* in, void* out, int tokens, int inter, int block,
 }
 
 int stride_scale_rows(const void* xtilde, const float* partials, int count, float eps, void* out, int tokens, int width,
-                      cudaStream_t stream) {
-    if (tokens < 0 || tokens > 16 || width <= 0 || count <= 0 || partials == nullptr) return STRIDE_BAD_ARGUMENT;
+                      int token_stride, cudaStream_t stream) {
+    if (tokens < 0 || tokens > token_stride || width <= 0 || count <= 0 || partials == nullptr) return STRIDE_BAD_ARGUMENT;
     if (tokens == 0) return 0;
     stride::launch(scale_rows_kernel, dim3(tokens), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(xtilde), partials, count, eps,
-                   static_cast<__nv_bfloat16*>(out), width);
+                   static_cast<__nv_bfloat16*>(out), width, token_stride);
     return STRIDE_LAUNCH_STATUS();
 }
 

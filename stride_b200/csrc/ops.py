@@ -44,13 +44,22 @@ _SIGNATURES = {
     "stride_gemm_tc_skinny": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong,
                                                c_void_p, c_int, c_void_p, c_void_p]),
     "stride_gemm_tc_clustered": ("gemm_bf16_tc", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "stride_gemm_rows": ("gemm_bf16_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "stride_gemm_rows_add": ("gemm_bf16_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "stride_gemm_rows_gated": ("gemm_bf16_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float,
+                                                  c_void_p, c_void_p]),
+    "stride_gemm_rows_qkv_rope": ("gemm_bf16_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                     c_int, c_float, c_void_p, c_void_p]),
+    "stride_gemm_rows_add_norm": ("gemm_bf16_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                                                     c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "stride_gemm_stream_bf16": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "stride_gemm_stream_qkv_rope": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                          c_void_p, c_int, c_float, c_void_p, c_void_p]),
     "stride_gemm_stream_add_norm": ("gemm_bf16_stream", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong,
                                                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "stride_scale_rows": ("elementwise", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_void_p]),
+    "stride_scale_rows": ("elementwise", [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p]),
     "stride_paged_decode_attention": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                            c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int,
                                                            c_float, c_int, c_int, c_void_p]),
@@ -311,7 +320,9 @@ def tc_status(device=None) -> int:
 
 
 _WAIT_CODES = {1: "matrix product: producer", 2: "matrix product: tensor-core issuer", 3: "matrix product: epilogue",
-               31: "decode attention: a tile copy", 41: "weight-streaming product: a tile copy"}
+               31: "decode attention: a tile copy", 41: "weight-streaming product: a tile copy",
+               51: "tokens-as-rows product: activation copies", 52: "tokens-as-rows product: weight copies",
+               53: "tokens-as-rows product: tensor-core issuer", 54: "tokens-as-rows product: epilogue"}
 _WAIT_CODES.update({c: "prefill attention (attention_prefill_tc.cu)" for c in range(11, 22)})
 _OTHER_CODES = {32: "decode attention was given a token whose position is not below the context bound of its launch"}
 
@@ -393,6 +404,113 @@ def linear_tc_clustered(x, weight, out) -> bool:
     return True
 
 
+# Decode steps of 17 to this many tokens run the package's tcgen05 product with the tokens as the rows of the tile
+# (gemm_bf16_rows.cu: one CTA per block of output features and all of K; residual sum and the statistics of the norm
+# that follows, the norm's factor, rotation with cache write and SiLU * up in its epilogues), up to 128 at the most.
+# Measured on the 8B sizes at a context of 2,048 (whole decode step from a graph, this kernel / library product with
+# separate elementwise kernels): 17 tokens 4.43 / 4.44 ms, 24: 4.70 / 4.63, 32: 4.92 / 4.97, 40: 5.60 / 5.28,
+# 64: 6.57 / 6.29, 128: 10.0 / 9.1. Every CTA reads all of the activations, and with 32 features a CTA that is more
+# than the weights from 33 tokens on; the library shares them between the CTAs of a cluster. So the default stops at 32.
+# STRIDE_ROWS_GEMM_MAX_TOKENS=0 sends all of them to the library product and the separate elementwise kernels.
+ROWS_GEMM_MAX_TOKENS = min(128, int(_os.environ.get("STRIDE_ROWS_GEMM_MAX_TOKENS", "32")))
+
+
+def rows_wanted(tokens: int) -> bool:
+    """Whether a step of this many tokens runs its products on the tokens-as-rows kernel (the callers' policy; the
+    ``linear_rows*`` functions themselves take up to 128 rows)."""
+    return TC_GEMM_MAX_TOKENS < tokens <= ROWS_GEMM_MAX_TOKENS
+
+
+def _rows_ok(x, m: int) -> bool:
+    return m <= 128 and x.dtype == torch.bfloat16 and TC_GEMM_MAX_TOKENS > 0
+
+
+def linear_rows(x, weight, out) -> bool:
+    """``out = x @ weight.T`` (bfloat16 or float32 out) for up to 128 rows of ``x`` on the tokens-as-rows tcgen05 kernel.
+    Returns False when the kernel does not take the shape."""
+    m, k = x.shape
+    n = weight.shape[0]
+    code = _fn("stride_gemm_rows", f"product {n}x{k} (tcgen05, tokens as rows)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out"), m, n, k,
+        int(out.dtype == torch.float32), _status_ptr(x.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_rows")
+    return True
+
+
+def linear_rows_add(x, weight, residual) -> bool:
+    """``residual += bf16(x @ weight.T)`` (float32 residual) in one kernel, for 17 to 128 rows. False: not done."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if not _rows_ok(x, m) or residual.shape != (m, n):
+        return False
+    code = _fn("stride_gemm_rows_add", f"product {n}x{k} (tcgen05, tokens as rows, + residual)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(residual, "residual", torch.float32), m, n, k,
+        _status_ptr(x.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_rows_add")
+    return True
+
+
+def linear_rows_add_norm(x, weight, residual, norm_weight, xt, partials) -> int:
+    """``linear_add_norm`` for 17 to 128 rows: ``partials[cta, token]`` has 128 tokens a CTA. Returns the number of
+    producer CTAs, or 0 when the kernel does not take the sizes."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (FOLD_NORMS and _rows_ok(x, m)) or residual.shape != (m, n):
+        return 0
+    count = c_int(0)
+    code = _fn("stride_gemm_rows_add_norm", f"product {n}x{k} (tcgen05, tokens as rows, + residual, norm statistics)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(xt, "xt", torch.bfloat16),
+        _dev(residual, "residual", torch.float32), _dev(norm_weight, "norm_weight", torch.float32),
+        _dev(partials, "partials", torch.float32), partials.numel(), m, n, k, ctypes.byref(count), _status_ptr(x.device), _stream())
+    if code == -2:
+        return 0
+    _check(code, "gemm_rows_add_norm")
+    return count.value
+
+
+ROWS_FOLD_STRIDE = 128      # tokens a CTA in the partials that ``linear_rows_add_norm`` writes
+
+
+def linear_rows_gated(x, weight, out, folded=None) -> bool:
+    """``out = silu(x @ gate.T) * (x @ up.T)`` for 17 to 128 rows; ``weight`` as for ``linear_gated_tc``; ``folded``: a
+    FoldedNorm from ``linear_rows_add_norm`` whose ``xt`` is ``x``. False: not done."""
+    m, k = x.shape
+    inter = weight.shape[0] // 2
+    if not _rows_ok(x, m) or out.shape != (m, inter) or (folded is not None and folded.stride != ROWS_FOLD_STRIDE):
+        return False
+    partials, count, eps = _fold_args(folded, ROWS_FOLD_STRIDE)
+    code = _fn("stride_gemm_rows_gated", f"product 2x{inter}x{k} (tcgen05, tokens as rows, silu * up)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(out, "out", torch.bfloat16), m, inter, k,
+        partials, count, eps, _status_ptr(x.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_rows_gated")
+    return True
+
+
+def linear_rows_qkv_rope(x, weight, qkv, bias, positions, slot_mapping, cos, sin, k_pages, v_pages, nq: int, nkv: int, hd: int,
+                         page_size: int, rotate: bool, folded=None) -> bool:
+    """``linear_qkv_rope`` for 17 to 128 rows of ``x`` (``folded``: from ``linear_rows_add_norm``). False: not done."""
+    m, k = x.shape
+    if not _rows_ok(x, m) or qkv.shape != (m, (nq + 2 * nkv) * hd) or (folded is not None and folded.stride != ROWS_FOLD_STRIDE):
+        return False
+    partials, count, eps = _fold_args(folded, ROWS_FOLD_STRIDE)
+    code = _fn("stride_gemm_rows_qkv_rope", f"product {weight.shape[0]}x{k} (tcgen05, tokens as rows, qkv + rotation + cache write)")(
+        _dev(x, "x", torch.bfloat16), _dev(weight, "weight", torch.bfloat16), _dev(qkv, "qkv", torch.bfloat16),
+        _opt(bias, "bias", torch.float32), _dev(positions, "positions", torch.int32), _opt(slot_mapping, "slot_mapping", torch.int32),
+        _dev(cos, "cos", torch.float32), _dev(sin, "sin", torch.float32), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), m, nq, nkv, hd, page_size, k, int(rotate), partials, count, eps,
+        _status_ptr(x.device), _stream())
+    if code == -2:
+        return False
+    _check(code, "gemm_rows_qkv_rope")
+    return True
+
+
 GATED_BLOCK = 64      # rows of gate and up alternate in blocks of this many in a weight laid out for ``linear_gated_tc``
 
 
@@ -402,11 +520,12 @@ FOLD_NORMS = _os.environ.get("STRIDE_B200_FOLD_NORMS", "1") != "0"
 class FoldedNorm:
     """The output of an RMS norm whose two halves were folded into the products around it: ``xt`` holds
     ``residual * weight`` in bfloat16 (no 1/rms yet), ``partials`` [count, 16] the sums of squares of the
-    residual per producer CTA and token. A product that takes it applies ``rsqrt(sum / width + eps)`` to its
+    residual per producer CTA and token (``stride`` tokens a CTA: 16 from the kernels for at most 16 tokens, 128 from
+    the tokens-as-rows kernel). A product that takes it applies ``rsqrt(sum / width + eps)`` to its
     accumulators; anything else asks for ``tensor()``, which runs the small kernel that finishes the norm."""
 
-    def __init__(self, xt, partials, count: int, eps: float, make_buffer):
-        self.xt, self.partials, self.count, self.eps = xt, partials, int(count), float(eps)
+    def __init__(self, xt, partials, count: int, eps: float, make_buffer, stride: int = 16):
+        self.xt, self.partials, self.count, self.eps, self.stride = xt, partials, int(count), float(eps), int(stride)
         self.shape, self.dtype, self.device = xt.shape, xt.dtype, xt.device
         self._make_buffer = make_buffer
         self._tensor = None
@@ -415,14 +534,16 @@ class FoldedNorm:
         if self._tensor is None:
             out = self._make_buffer()
             _check(_fn("stride_scale_rows")(self.xt.data_ptr(), self.partials.data_ptr(), self.count, self.eps, out.data_ptr(),
-                                            self.shape[0], self.shape[1], _stream()), "scale_rows")
+                                            self.shape[0], self.shape[1], self.stride, _stream()), "scale_rows")
             self._tensor = out
         return self._tensor
 
 
-def _fold_args(folded):
+def _fold_args(folded, stride: int = 16):
     if folded is None:
         return None, 0, 0.0
+    if folded.stride != stride:
+        raise ValueError(f"a folded norm with {folded.stride} tokens a CTA was given to a kernel that reads {stride}")
     return folded.partials.data_ptr(), folded.count, folded.eps
 
 

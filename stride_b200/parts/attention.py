@@ -98,13 +98,17 @@ class PagedAttention(Mixer):
     def _project_and_rotate(self, x, qkv, ctx, cache, tokens, folded=None) -> bool:
         """A decode step's projection with the position encoding and the cache write in its epilogue, when the
         position part says that what it does is the standard rotation. False: nothing was done."""
-        if tokens > ops.TC_GEMM_MAX_TOKENS or x.dtype != torch.bfloat16:
+        if tokens > max(ops.TC_GEMM_MAX_TOKENS, ops.ROWS_GEMM_MAX_TOKENS) or x.dtype != torch.bfloat16:
             return False
         tables = self.position.rotation_tables()
         if tables is None:
             return False
         cos, sin, rotate = tables
         slots = ctx.slot_mapping[cache.group][:tokens] if cache.writes else None
+        if tokens > ops.TC_GEMM_MAX_TOKENS:         # the tokens-as-rows kernel, where the policy sends steps of this size to it
+            return ops.rows_wanted(tokens) and ops.linear_rows_qkv_rope(
+                x, self.w_qkv, qkv, self.bias, ctx.positions[:tokens], slots, cos, sin, cache.k_pages, cache.v_pages, self.nq, self.nkv,
+                self.hd, cache.page_size, rotate, folded)
         return ops.linear_qkv_rope(x, self.w_qkv, qkv, self.bias, ctx.positions[:tokens], slots, cos, sin, cache.k_pages,
                                    cache.v_pages, self.nq, self.nkv, self.hd, cache.page_size, rotate, folded)
 

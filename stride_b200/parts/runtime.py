@@ -85,7 +85,10 @@ class ResidualStream:
     def _settle(self) -> None:
         """Applies what is pending to the residual."""
         if self._pending is not None:
-            ops.add_residual(self.residual, self._run(self._pending))
+            p = self._pending
+            if not (isinstance(p, Projection) and p.weight.shape[0] == self.hidden and ops.rows_wanted(self.tokens)
+                    and ops.linear_rows_add(p.x, p.weight, self.residual)):
+                ops.add_residual(self.residual, self._run(p))
             self._pending = None
 
     def _run(self, pending):
@@ -106,6 +109,9 @@ class ResidualStream:
             folded = self._fold(norm, tag)
             if folded is not None:
                 return folded
+        if rows is None and isinstance(self._pending, Projection) and self._pending.weight.shape[0] == self.hidden and \
+                ops.rows_wanted(self.tokens) and ops.linear_rows_add(self._pending.x, self._pending.weight, self.residual):
+            self._pending = None        # the tokens-as-rows product added itself to the residual stream
         pending = None if self._pending is None else self._run(self._pending)
         if rows is None:
             out = self.rt.buffer(tag, self.tokens, self.hidden)
@@ -126,12 +132,15 @@ class ResidualStream:
         if p.weight.shape[0] != self.hidden:
             return None
         xt = self.rt.buffer(tag + "_folded", self.tokens, self.hidden)
-        partials = self.rt.scratch("norm_partials", 16 * 1024)
+        partials = self.rt.scratch("norm_partials", max(16 * 1024, self.hidden // 32 * ops.ROWS_FOLD_STRIDE))
+        stride = 16
         count = ops.linear_add_norm(p.x, p.weight, self.residual, weight, xt, partials)
+        if not count and ops.rows_wanted(self.tokens):
+            count, stride = ops.linear_rows_add_norm(p.x, p.weight, self.residual, weight, xt, partials), ops.ROWS_FOLD_STRIDE
         if not count:
             return None
         self._pending = None
-        return ops.FoldedNorm(xt, partials, count, eps, lambda: self.rt.buffer(tag, self.tokens, self.hidden))
+        return ops.FoldedNorm(xt, partials, count, eps, lambda: self.rt.buffer(tag, self.tokens, self.hidden), stride)
 
     def materialize(self):
         """The stream with every pending sum applied (float32)."""

@@ -58,7 +58,10 @@ class SwiGLU(FeedForward):
         tokens = x.shape[0]
         act = self.rt.buffer("ffn_act", tokens, self.inter)
         folded = x if isinstance(x, ops.FoldedNorm) else None
-        if not (self.block == ops.GATED_BLOCK and ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded)):
+        gated = self.block == ops.GATED_BLOCK and (
+            ops.linear_gated_tc(folded.xt if folded else x, self.w_gate_up, act, folded)
+            or (ops.rows_wanted(tokens) and ops.linear_rows_gated(folded.xt if folded else x, self.w_gate_up, act, folded)))
+        if not gated:
             if folded:
                 x = folded.tensor()
             gate_up = self.rt.buffer("gate_up", tokens, 2 * self.inter)

@@ -431,6 +431,170 @@ def test_the_clustered_product_for_17_to_64_tokens(ops, tokens, n, k):
             assert err <= tol * scale, f"{out_dtype}: max abs error {err:.3e} against scale {scale:.3e}"
 
 
+@pytest.mark.parametrize("tokens,n,k", [(17, 4096, 4096), (33, 6144, 4096), (64, 4096, 14336), (100, 28672, 1024), (128, 1000, 520),
+                                        (40, 384, 64), (20, 128256, 1024), (64, 8192, 8192)])
+def test_the_tokens_as_rows_product(ops, tokens, n, k):
+    """The tcgen05 product whose tile rows are the tokens (17 to 128 of them), one CTA per block of 32, 64 or 128 output
+    features and all of K, two issuing warps with an accumulator each: feature counts that fill no whole block, one
+    block of K and hundreds, float32 and bfloat16 results, the residual sum in the epilogue; nothing is written past
+    the last token."""
+    g = torch.Generator().manual_seed(tokens + n)
+    x = (torch.randn(tokens, k, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    w[min(n - 1, 130), :] = w[min(n - 1, 130), :] * 8       # one feature stands out: a block that is dropped shows
+    want = x.double() @ w.double().T
+    scale = float(want.abs().max())
+    for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((tokens + 3, n), 7.0, dtype=out_dtype, device="cuda")
+        assert ops.linear_rows(dev(x), dev(w), out[:tokens]), "the kernel refused the shape"
+        ops.check_kernel_status()
+        err = float((out[:tokens].double().cpu() - want).abs().max())
+        assert err <= tol * scale, f"{out_dtype}: max abs error {err:.3e} against scale {scale:.3e}"
+        assert float(out[tokens:].min()) == 7.0 and float(out[tokens:].max()) == 7.0, "the kernel wrote past the last token"
+    # residual += bf16(product), in float32
+    residual = torch.randn(tokens, n, generator=g)
+    got = dev(residual.clone())
+    assert ops.linear_rows_add(dev(x), dev(w), got)
+    ops.check_kernel_status()
+    plain_sum = residual.double() + want.bfloat16().double()
+    assert float((got.double().cpu() - plain_sum).abs().max()) <= 1e-2 * scale
+    bf = torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_rows(dev(x), dev(w), bf)
+    assert torch.equal(got, dev(residual) + bf.float()), "the fused residual sum differs from product, then sum"
+
+
+@pytest.mark.parametrize("tokens,inter,k", [(17, 14336, 4096), (64, 8192, 3072), (128, 320, 192), (33, 64, 64)])
+def test_the_tokens_as_rows_product_with_gate_epilogue(ops, tokens, inter, k):
+    from stride_b200.parts.swiglu import interleave_gate_up
+    g = torch.Generator().manual_seed(35)
+    x = (torch.randn(tokens, k, generator=g) * 0.5).bfloat16()
+    gate = (torch.randn(inter, k, generator=g) * 0.05).bfloat16()
+    up = (torch.randn(inter, k, generator=g) * 0.05).bfloat16()
+    w = dev(interleave_gate_up(gate, up, ops.GATED_BLOCK))
+    out = torch.full((tokens, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_rows_gated(dev(x), w, out)
+    ops.check_kernel_status()
+    gu = torch.empty(tokens, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_rows(dev(x), w, gu)
+    unfused = torch.empty_like(out)
+    ops.silu_mul(gu, unfused, ops.GATED_BLOCK)
+    gd, ud = (x.double() @ gate.double().T), (x.double() @ up.double().T)
+    want = gd * torch.sigmoid(gd) * ud
+    close(out, want, torch.bfloat16)
+    close(out, unfused.double(), torch.bfloat16)
+
+
+@pytest.mark.parametrize("tokens,nq,nkv,hd,k,page,bias,rotate", [
+    (64, 32, 8, 128, 4096, 16, False, True), (17, 4, 4, 64, 256, 16, True, True), (100, 6, 2, 128, 200, 8, False, True),
+    (33, 4, 1, 128, 192, 32, True, False), (128, 3, 1, 64, 96, 16, False, True),
+])
+def test_the_tokens_as_rows_projection_with_rotation_and_cache_write(ops, tokens, nq, nkv, hd, k, page, bias, rotate):
+    """The fused kernel against the same product followed by ``rope_kv_write`` (itself tested against float64): bit for bit."""
+    g = torch.Generator().manual_seed(36)
+    heads = nq + 2 * nkv
+    x = dev((torch.randn(tokens, k, generator=g) * 0.5).bfloat16())
+    w = dev((torch.randn(heads * hd, k, generator=g) * 0.05).bfloat16())
+    b = dev(torch.randn(heads * hd, generator=g) * 0.1) if bias else None
+    num_pages, max_pos = 40, 700
+    positions = dev(torch.randint(0, max_pos, (tokens,), generator=g).to(torch.int32))
+    slots = torch.randperm(num_pages * page, generator=g)[:tokens].to(torch.int32)
+    slots[tokens - 1] = -1                       # a padded token stores nothing
+    slots = dev(slots)
+    inv = plain.rope_inv_freq(hd, 25000.0, None)
+    angles = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    cos, sin = dev(angles.cos()), dev(angles.sin())
+
+    def run(fused):
+        k_pages = torch.full((num_pages, nkv, page, hd), 3.0, dtype=torch.bfloat16, device="cuda")
+        v_pages = torch.full_like(k_pages, 3.0)
+        qkv = torch.full((tokens, heads * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            assert ops.linear_rows_qkv_rope(x, w, qkv, b, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, rotate)
+        else:
+            assert ops.linear_rows(x, w, qkv)
+            ops.rope_kv_write(qkv, b, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, rotate=rotate)
+        ops.check_kernel_status()
+        return qkv[:, :nq * hd].clone(), k_pages, v_pages
+
+    q1, k1, v1 = run(True)
+    q0, k0, v0 = run(False)
+    assert torch.equal(q1, q0) and torch.equal(k1, k0) and torch.equal(v1, v0), "the fused projection differs from product + rope_kv_write"
+    assert float(k1.float().sub(3.0).abs().max()) > 0.0     # something was stored
+
+
+@pytest.mark.parametrize("tokens,hidden,k,inter", [(17, 4096, 4096, 14336), (64, 1024, 2048, 1024), (128, 192, 512, 320), (40, 8192, 1024, 128)])
+def test_rms_norm_folded_into_the_tokens_as_rows_products(ops, tokens, hidden, k, inter):
+    """As for at most 16 tokens: the product before the norm adds to the residual and leaves x~ and the sums of
+    squares of its columns per CTA (128 tokens a CTA), the products after it apply 1/rms to their accumulators."""
+    from stride_b200.parts.swiglu import interleave_gate_up
+    g = torch.Generator().manual_seed(37)
+    x = dev(torch.randn(tokens, k, generator=g).bfloat16())
+    w = dev((torch.randn(hidden, k, generator=g) * 0.05).bfloat16())
+    residual0 = torch.randn(tokens, hidden, generator=g) * 3
+    residual0[tokens - 1] *= 40                   # one token far larger than the others: a factor taken from another row shows
+    norm_w = dev(1 + 0.1 * torch.randn(hidden, generator=g))
+    eps = 1e-5
+    delta = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_rows(x, w, delta)
+    res_a = dev(residual0.clone())
+    normed = torch.empty_like(delta)
+    ops.add_rmsnorm(res_a, delta, norm_w, normed, eps)
+    res_b = dev(residual0.clone())
+    xt = torch.empty_like(delta)
+    partials = torch.full((max(16 * 1024, hidden // 32 * 128),), float("nan"), device="cuda")
+    count = ops.linear_rows_add_norm(x, w, res_b, norm_w, xt, partials)
+    assert count > 0, "the kernel refused sizes it should take"
+    ops.check_kernel_status()
+    assert torch.equal(res_a, res_b), "the residual stream differs"
+    folded = ops.FoldedNorm(xt, partials, count, eps, lambda: torch.empty_like(delta), ops.ROWS_FOLD_STRIDE)
+    want = res_a.double() * torch.rsqrt((res_a.double() ** 2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    for t in range(tokens):     # row by row: the rows differ in size by a factor of 40
+        close(folded.tensor()[t], want[t], torch.bfloat16)
+    if inter % 64 == 0:
+        gate = (torch.randn(inter, hidden, generator=g) * 0.05).bfloat16()
+        up = (torch.randn(inter, hidden, generator=g) * 0.05).bfloat16()
+        wgu = dev(interleave_gate_up(gate, up, ops.GATED_BLOCK))
+        plain_out = torch.empty(tokens, inter, dtype=torch.bfloat16, device="cuda")
+        fold_out = torch.empty_like(plain_out)
+        assert ops.linear_rows_gated(normed, wgu, plain_out)
+        assert ops.linear_rows_gated(xt, wgu, fold_out, folded)
+        ops.check_kernel_status()
+        gd, ud = want @ dev(gate).double().T, want @ dev(up).double().T       # from the norm in float64
+        truth = gd * torch.sigmoid(gd) * ud
+        for t in range(tokens):
+            close(plain_out[t], truth[t], torch.bfloat16)
+            close(fold_out[t], truth[t], torch.bfloat16)
+    if hidden % 128 == 0:
+        nq, nkv, hd, page = max(1, hidden // 256), 1, 128, 16
+        heads = nq + 2 * nkv
+        wqkv = dev((torch.randn(heads * hd, hidden, generator=g) * 0.05).bfloat16())
+        positions = dev(torch.arange(tokens, dtype=torch.int32) * 3)
+        slots = dev(torch.arange(tokens, dtype=torch.int32))
+        inv = plain.rope_inv_freq(hd, 10000.0, None)
+        angles = torch.outer(torch.arange(3 * tokens + 1, dtype=torch.float32), inv)
+        cos, sin = dev(angles.cos()), dev(angles.sin())
+        results = []
+        for source, fold in ((normed, None), (xt, folded)):
+            k_pages = torch.zeros(tokens // page + 1, nkv, page, hd, dtype=torch.bfloat16, device="cuda")
+            v_pages = torch.zeros_like(k_pages)
+            qkv = torch.zeros(tokens, heads * hd, dtype=torch.bfloat16, device="cuda")
+            assert ops.linear_rows_qkv_rope(source, wqkv, qkv, None, positions, slots, cos, sin, k_pages, v_pages, nq, nkv, hd, page, True, fold)
+            ops.check_kernel_status()
+            results.append((qkv[:, :nq * hd].clone(), k_pages, v_pages))
+        for a, b in zip(results[0], results[1]):
+            close(b, a.double(), torch.bfloat16, scale=float(results[0][0].double().abs().max()))
+
+
+def test_the_tokens_as_rows_product_refuses_what_it_cannot_run(ops):
+    x = torch.zeros(129, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.linear_rows(x, w, torch.zeros(129, 128, dtype=torch.bfloat16, device="cuda"))              # more than 128 tokens
+    assert not ops.linear_rows(x[:20, :60].contiguous(), w[:, :60].contiguous(), torch.zeros(20, 128, dtype=torch.bfloat16, device="cuda"))   # k % 8
+    assert not ops.linear_rows_gated(x[:20], torch.zeros(2 * 96, 64, dtype=torch.bfloat16, device="cuda"),
+                                     torch.zeros(20, 96, dtype=torch.bfloat16, device="cuda"))                # inner % 64
+    assert not ops.rows_wanted(8) and not ops.rows_wanted(129)       # the callers' policy: other kernels take few tokens, the library many
+
+
 def test_decode_attention_refuses_a_position_beyond_the_bound_of_its_launch(ops):
     """A launch is sized for positions below ``max_context``. A row beyond it would wait for splits that were never
     launched; it gets zeros and a code in the status word instead, and leaves no ticket behind: the next launch on

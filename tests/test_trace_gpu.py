@@ -151,7 +151,8 @@ def test_decoding_across_context_buckets(case, monkeypatch):
 @pytest.mark.parametrize("live", [20, 33, 64])
 def test_many_requests_decoding_together(case, dtype, live):
     """Up to 64 requests live at once, all decoding in the same steps: the decode graphs for 32 and 64 rows, where
-    the bfloat16 products go to the library and norm, rotation and SiLU run as kernels of their own."""
+    the bfloat16 products go to the library and norm, rotation and SiLU run as kernels of their own (17 to 32 rows:
+    the package's own tokens-as-rows products)."""
     from stride_b200.engine.trace import TraceSession
     vocab = case["cfg"]["vocab_size"]
     requests = {f"r{i}": seeded_tokens(9 + (i * 7) % 41, vocab, 3000 + i) for i in range(live)}
@@ -164,6 +165,24 @@ def test_many_requests_decoding_together(case, dtype, live):
     check(got, want, dtype, f"{live} requests decoding together")
     assert session.runner.graph_replays >= 7, "the decode steps did not go through captured graphs"
     assert max(session.runner.captured_buckets()) >= min(live, 64)
+
+
+@pytest.mark.parametrize("live", [33, 64, 100])
+def test_many_requests_decoding_together_on_the_tokens_as_rows_products(case, live, monkeypatch):
+    """The package's own tcgen05 products with fused epilogues take decode steps of 17 to 32 tokens by default; here
+    they take all steps up to 128 tokens, so that the graphs of 64 and 128 rows run them too."""
+    from stride_b200.csrc import ops
+    from stride_b200.engine.trace import TraceSession
+    monkeypatch.setattr(ops, "ROWS_GEMM_MAX_TOKENS", 128)
+    vocab = case["cfg"]["vocab_size"]
+    requests = {f"r{i}": seeded_tokens(9 + (i * 7) % 41, vocab, 3000 + i) for i in range(live)}
+    _, state = read_model_dir(case["dirs"]["bfloat16"])
+    want = {rid: plain.forward(case["cfg"], state, t, torch.float64) for rid, t in requests.items()}
+    steps = modes.decoding_together(requests, decode_steps=6)
+    session = TraceSession(case["dirs"]["bfloat16"], "bfloat16", max_tokens=modes.peak_tokens(steps), block_size=case["page"], max_requests=live)
+    got = replay(session, steps)
+    check(got, want, "bfloat16", f"{live} requests decoding together on the tokens-as-rows products")
+    assert session.runner.graph_replays >= 5, "the decode steps did not go through captured graphs"
 
 
 def test_an_unknown_token_or_too_few_pages_is_an_error_not_a_wrong_result(case):
