@@ -118,17 +118,18 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     // "all but the newest group have landed" means the same thing in every iteration.
     auto issue = [&](int j) {
         if (TMA) {
-            if (tile_live(j) && alive && lane == 0) {
+            // One thread needs 100 to 300 cycles per TMA instruction; executed by several lanes at once, each with
+            // its own box, the instruction costs the warp no more. Lane b < 2 HALVES copies box b: keys or values
+            // (b & 1), columns 64 (b >> 1) .. of the head. The barrier's pending arrival (lane 0's, with the byte
+            // count) keeps the phase open whichever lane's copy lands first.
+            if (tile_live(j) && alive && lane < 2 * HALVES) {
                 const int key0 = tile_base(j);                        // a multiple of 16: the tile lies inside one page
                 const int y = (table[key0 / page_size] * nkv + kvh) * page_size + key0 % page_size;
                 const uint32_t bar = tc::smem_u32(&tile_bar[warp][j % kStages]);
-                const uint32_t ks = tc::smem_u32(k_stage(j % kStages)), vs = ks + TILE_BYTES;
-                tc::mbar_expect_tx(bar, 2 * TILE_BYTES);
-#pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tc::tma_load_2d(ks + h * BOX_BYTES, &map_k, bar, h * 64, y);
-                    tc::tma_load_2d(vs + h * BOX_BYTES, &map_v, bar, h * 64, y);
-                }
+                const uint32_t ks = tc::smem_u32(k_stage(j % kStages));
+                if (lane == 0) tc::mbar_expect_tx(bar, 2 * TILE_BYTES);
+                const int h = lane >> 1;
+                tc::tma_load_2d(ks + (lane & 1) * TILE_BYTES + h * BOX_BYTES, (lane & 1) ? &map_v : &map_k, bar, h * 64, y);
             }
             return;
         }

@@ -404,15 +404,16 @@ def linear_tc_clustered(x, weight, out) -> bool:
     return True
 
 
-# Decode steps of 17 to this many tokens run the package's tcgen05 product with the tokens as the rows of the tile
-# (gemm_bf16_rows.cu: one CTA per block of output features and all of K; residual sum and the statistics of the norm
-# that follows, the norm's factor, rotation with cache write and SiLU * up in its epilogues), up to 128 at the most.
-# Measured on the 8B sizes at a context of 2,048 (whole decode step from a graph, this kernel / library product with
-# separate elementwise kernels): 17 tokens 4.43 / 4.44 ms, 24: 4.70 / 4.63, 32: 4.92 / 4.97, 40: 5.60 / 5.28,
-# 64: 6.57 / 6.29, 128: 10.0 / 9.1. Every CTA reads all of the activations, and with 32 features a CTA that is more
-# than the weights from 33 tokens on; the library shares them between the CTAs of a cluster. So the default stops at 32.
-# STRIDE_ROWS_GEMM_MAX_TOKENS=0 sends all of them to the library product and the separate elementwise kernels.
-ROWS_GEMM_MAX_TOKENS = min(128, int(_os.environ.get("STRIDE_ROWS_GEMM_MAX_TOKENS", "32")))
+# Decode steps of 17 to this many tokens (128 at the most) run the package's tcgen05 product with the tokens as the
+# rows of the tile (gemm_bf16_rows.cu: one CTA per block of output features and all of K; residual sum and the
+# statistics of the norm that follows, the norm's factor, rotation with cache write and SiLU * up in its epilogues).
+# Off by default: it is level with the library product plus separate elementwise kernels where a 4096-row matrix
+# gives every SM a CTA, and slower elsewhere. Whole decode steps from a graph, this kernel / library: 8B sizes at a
+# context of 2,048, 17 tokens 4.43 / 4.44 ms, 24: 4.70 / 4.63, 32: 4.92 / 4.97, 40: 5.60 / 5.28, 64: 6.57 / 6.29,
+# 128: 10.0 / 9.1; at a context of 1,024, 32 tokens 4.33 / 4.42; 3B sizes (3072-row matrices: 96 CTAs), 32 tokens at
+# a context of 4,096 4.50 / 4.28. Every CTA reads all of the activations, which is more than its weights once there
+# are more tokens than features in its block; the library shares them between the CTAs of a cluster.
+ROWS_GEMM_MAX_TOKENS = min(128, int(_os.environ.get("STRIDE_ROWS_GEMM_MAX_TOKENS", "0")))
 
 
 def rows_wanted(tokens: int) -> bool:

@@ -151,8 +151,7 @@ def test_decoding_across_context_buckets(case, monkeypatch):
 @pytest.mark.parametrize("live", [20, 33, 64])
 def test_many_requests_decoding_together(case, dtype, live):
     """Up to 64 requests live at once, all decoding in the same steps: the decode graphs for 32 and 64 rows, where
-    the bfloat16 products go to the library and norm, rotation and SiLU run as kernels of their own (17 to 32 rows:
-    the package's own tokens-as-rows products)."""
+    the bfloat16 products go to the library and norm, rotation and SiLU run as kernels of their own."""
     from stride_b200.engine.trace import TraceSession
     vocab = case["cfg"]["vocab_size"]
     requests = {f"r{i}": seeded_tokens(9 + (i * 7) % 41, vocab, 3000 + i) for i in range(live)}
@@ -167,13 +166,20 @@ def test_many_requests_decoding_together(case, dtype, live):
     assert max(session.runner.captured_buckets()) >= min(live, 64)
 
 
-@pytest.mark.parametrize("live", [33, 64, 100])
+@pytest.mark.parametrize("live", [20, 33, 64, 100])
 def test_many_requests_decoding_together_on_the_tokens_as_rows_products(case, live, monkeypatch):
-    """The package's own tcgen05 products with fused epilogues take decode steps of 17 to 32 tokens by default; here
-    they take all steps up to 128 tokens, so that the graphs of 64 and 128 rows run them too."""
+    """The package's own tcgen05 products with fused epilogues for 17 to 128 tokens are off by default (the library
+    product is as fast or faster); here they take every decode step of more than 16 tokens."""
     from stride_b200.csrc import ops
     from stride_b200.engine.trace import TraceSession
     monkeypatch.setattr(ops, "ROWS_GEMM_MAX_TOKENS", 128)
+    taken = {}
+    for name in ("linear_rows_qkv_rope", "linear_rows_add_norm", "linear_rows_gated"):
+        def counted(*args, _f=getattr(ops, name), _name=name, **kwargs):
+            done = _f(*args, **kwargs)
+            taken[_name] = taken.get(_name, 0) + bool(done)
+            return done
+        monkeypatch.setattr(ops, name, counted)
     vocab = case["cfg"]["vocab_size"]
     requests = {f"r{i}": seeded_tokens(9 + (i * 7) % 41, vocab, 3000 + i) for i in range(live)}
     _, state = read_model_dir(case["dirs"]["bfloat16"])
@@ -182,6 +188,8 @@ def test_many_requests_decoding_together_on_the_tokens_as_rows_products(case, li
     session = TraceSession(case["dirs"]["bfloat16"], "bfloat16", max_tokens=modes.peak_tokens(steps), block_size=case["page"], max_requests=live)
     got = replay(session, steps)
     check(got, want, "bfloat16", f"{live} requests decoding together on the tokens-as-rows products")
+    if case["name"] == "D":       # its sizes are the kernels': all three must have run, with the norms folded into them
+        assert all(taken.get(n, 0) > 0 for n in ("linear_rows_qkv_rope", "linear_rows_add_norm", "linear_rows_gated")), taken
     assert session.runner.graph_replays >= 5, "the decode steps did not go through captured graphs"
 
 
