@@ -17,7 +17,9 @@ a batch of 8 requests at a context of 8192 tokens. It prints ONE JSON line:
   the measured copy bandwidth;
 * ``points``: decode at batch 1 and 64 at the run's context, and at batch 1, 8 and
   64 at a context of 2,048 (``--points`` chooses other batches; the page pool is
-  sized for what the run holds at once);
+  sized for what the run holds at once); also two more prefill steps of 2,048
+  tokens (tokens a second): the first 256 tokens of eight prompts in one step,
+  and 2,048 tokens of a prompt over 6,144 tokens that are already cached;
 * ``breakdown``: device time per class of kernel of one decode step and of the
   prefill, from CUDA events around every launch of an eagerly run step.
 
@@ -279,8 +281,37 @@ def run_ours(args) -> dict:
                "frac": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                "frac_of_burst_peak": round(prefill_flops(cfg, prompt_len) / (prefill_ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
 
+    # ---- two more prefill steps of 2,048 tokens: eight prompts' portions of 256 tokens in one step, and the last portion
+    # of an 8,192-token prompt (2,048 tokens over 6,144 cached ones), when the run's context has room for it
+    def portion_step(requests):
+        """Median device time (ms) of one step with the given (cached tokens, new tokens) per request."""
+        took = []
+        for i in range(2 + 3):
+            sb, keys = engine._rt.StepBatch(engine.cache), []
+            for j, (cached, new) in enumerate(requests):
+                key = 700000 + 100 * i + j
+                engine.cache.open(key, "bench")
+                engine.cache.ensure(key, cached + new, 0)
+                sb.add(key, prompt[:new], cached, [new - 1])
+                keys.append(key)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            engine.runner.step(sb)
+            end.record()
+            torch.cuda.synchronize()
+            for key in keys:
+                engine.cache.close(key)
+            if i >= 2:
+                took.append(start.elapsed_time(end))
+        return statistics.median(took)
+
+    prefill_points = {"prefill_8x256": round(prompt_len / portion_step([(0, prompt_len // 8)] * 8) * 1e3, 1)}
+    if context >= 8192:
+        prefill_points["prefill_2048_after_6144"] = round(prompt_len / portion_step([(6144, prompt_len)]) * 1e3, 1)
+
     # ---- decode points, device-timed graph replays on synthetic caches
-    points, key_base = {}, 1000
+    points, key_base = dict(prefill_points), 1000
     main = None
     runs = [(b, context) for b in point_batches if b != batch] + [(batch, context)]
     if short_context:
