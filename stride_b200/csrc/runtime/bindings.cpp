@@ -187,6 +187,16 @@ PYBIND11_MODULE(_runtime, m) {
         .def("next_u64", &Rng::next_u64)
         .def("next_f32", &Rng::next_f32);
 
+    m.def("rank_head",
+          [](py::array_t<float, py::array::c_style | py::array::forcecast> weights, std::optional<uint32_t> top_k, float top_p) {
+              std::vector<float> work(weights.data(), weights.data() + weights.size());
+              std::vector<uint32_t> order;
+              const size_t keep = rank_head(work, top_k, top_p, order);
+              order.resize(keep);
+              return order;
+          },
+          py::arg("weights"), py::arg("top_k") = py::none(), py::arg("top_p") = 1.0f,
+          "The tokens a draw keeps, in the order in which it walks them (see sampler.hpp).");
     py::class_<Sampler>(m, "Sampler")
         .def(py::init<SamplingParams, int32_t, uint64_t>(), py::arg("params"), py::arg("eos"), py::arg("fallback_seed"))
         .def_property_readonly("params", &Sampler::params)

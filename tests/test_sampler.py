@@ -41,6 +41,34 @@ def test_sampler_follows_the_reference_rules(kwargs):
     assert s.effective_seed == 11 and Sampler(SamplingParams(), 4, 99).effective_seed == 99
 
 
+@pytest.mark.parametrize("top_k,top_p", [(None, 0.95), (None, 0.3), (50, 1.0), (700, 0.99), (None, 0.999), (40000, 1.0), (1, 0.5)])
+def test_the_head_of_the_ranking_is_that_of_a_stable_sort(top_k, top_p):
+    """The sampler selects and sorts only the head of the ranking (the first 256 entries, then eight times as many,
+    as far as the nucleus reaches). Against a stable sort of the whole vocabulary with the same float32 sums: flat
+    rows whose nucleus holds most of the vocabulary, peaked rows, coarse weights with many ties (ties go by
+    vocabulary order, also across the edge of a head), all equal."""
+    from stride_b200.csrc.build import load_runtime
+    rank_head = load_runtime().rank_head
+    g = torch.Generator().manual_seed(5)
+    n = 30011
+    rows = [torch.softmax(torch.randn(n, generator=g) * 0.3, 0), torch.softmax(torch.randn(n, generator=g) * 6, 0),
+            torch.softmax(torch.round(torch.randn(n, generator=g) * 2) / 2, 0), torch.full((n,), 1.0 / n),
+            torch.softmax(torch.cat([torch.full((300,), 3.0), torch.zeros(n - 300)]), 0)]
+    for row in rows:
+        w = row.numpy().astype(np.float32)
+        order = np.argsort(-w, kind="stable")
+        limit = n if top_k is None else min(n, top_k)
+        keep = limit
+        if top_p < 1.0:
+            sums = np.cumsum(w[order], dtype=np.float32)          # sequential float32 additions, as the sampler's
+            reached = np.nonzero(sums >= np.float32(top_p))[0]
+            nucleus = int(reached[0]) + 1 if len(reached) else n
+            keep = min(limit, max(nucleus, 1))
+        got = rank_head(w, top_k, top_p)
+        assert len(got) == keep, f"keeps {len(got)} tokens, a full sort keeps {keep}"
+        assert np.array_equal(np.asarray(got), order[:keep]), "the kept ranking differs from a stable sort's"
+
+
 def test_eos_suppression_stop_tokens_and_extremes():
     logits = np.array([0.0, 5.0, 1.0, 4.0], dtype=np.float32)
     s = Sampler(SamplingParams(temperature=0.0, min_tokens=2, max_tokens=4, stop_tokens=[3]), eos=1, fallback_seed=0)
