@@ -72,6 +72,8 @@ _SIGNATURES = {
     "stride_paged_prefill_attention_tc": ("attention_prefill_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                                    c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
+    "stride_sample_ranked": ("sampling_ranked", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p, c_longlong, c_void_p]),
     "stride_sample_rows": ("sampling", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_longlong, c_void_p]),
 }
@@ -97,7 +99,7 @@ _CLASS_OF = {
     "stride_scale_rows": "norm", "stride_zero_fresh_state": "state slots", "stride_rope_kv_write": "rotation + cache write",
     "stride_silu_mul": "silu * up", "stride_paged_attention_generic": "attention (exact kernel)",
     "stride_paged_decode_attention_tma": "attention (decode)", "stride_paged_prefill_attention": "attention (prefill, mma.sync)",
-    "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling",
+    "stride_paged_prefill_attention_tc": "attention (prefill, tcgen05)", "stride_sample_rows": "sampling", "stride_sample_ranked": "sampling",
 }
 
 
@@ -785,3 +787,26 @@ def sample_rows(logits, out, temperature=None, uniform=None, suppress=None) -> N
                                      _opt(temperature, "temperature", torch.float32),
                                      _opt(uniform, "uniform", torch.float32), _opt(suppress, "suppress", torch.int32),
                                      _dev(out, "out", torch.int32), scratch.data_ptr(), scratch.numel(), _stream()), "sample_rows")
+
+
+_ranked_probs: dict = {}
+
+
+def sample_ranked(logits, out, temperature, uniform, suppress, top_k, top_p) -> None:
+    """Draws the rows with a temperature above 0 that ask for top-k (``top_k[r] > 0``) or a nucleus (``top_p[r] < 1``)
+    by the reference sampler's rule and writes their tokens to ``out``; the other rows of ``out`` are left as they
+    are (``sample_rows`` draws those). One [rows, vocab] float32 scratch per device, grown when a step needs more."""
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("logits rows must be dense")
+    if not logits.is_cuda:
+        raise KernelError("logits must live on a CUDA device; stride_b200 has no CPU path")
+    key = _device_key(logits.device)
+    probs = _ranked_probs.get(key)
+    if probs is None or probs.numel() < rows * vocab:
+        probs = torch.empty(rows * vocab, dtype=torch.float32, device=logits.device)
+        _ranked_probs[key] = probs
+    _check(_fn("stride_sample_ranked")(logits.data_ptr(), rows, vocab, logits.stride(0), _dev(temperature, "temperature", torch.float32),
+                                       _dev(uniform, "uniform", torch.float32), _opt(suppress, "suppress", torch.int32),
+                                       _dev(top_k, "top_k", torch.int32), _dev(top_p, "top_p", torch.float32),
+                                       _dev(out, "out", torch.int32), probs.data_ptr(), probs.numel(), _stream()), "sample_ranked")

@@ -334,6 +334,92 @@ def test_sample_rows_greedy_takes_the_first_maximum_and_honours_suppression(ops)
     assert out.tolist() == want == [5, 1002, 0, 78, 400, int(logits[5].argmax())]
 
 
+def _ranked_reference(logits_row, t, top_k, top_p, banned):
+    """The reference sampler's rule in float64 on the float32 scaled logits: (ranking, cumulated kept mass)."""
+    x = logits_row.clone().float()
+    if banned >= 0:
+        x[banned] = float("-inf")
+    if abs(t - 1.0) > 1.1920929e-07:
+        x = x / t
+    if torch.isinf(x).all():
+        probs = torch.full_like(x, 1.0 / x.numel(), dtype=torch.float64)
+    else:
+        probs = torch.softmax(x.double(), 0)
+    order = torch.argsort(-probs, stable=True)
+    keep = x.numel() if not top_k else min(x.numel(), top_k)
+    sorted_p = probs[order]
+    if top_p < 1.0:
+        cum_all = torch.cumsum(sorted_p, 0)
+        reached = torch.nonzero(cum_all >= top_p)
+        nucleus = int(reached[0]) + 1 if len(reached) else x.numel()
+        keep = min(keep, max(nucleus, 1))
+    return order[:keep], torch.cumsum(sorted_p[:keep], 0)
+
+
+@pytest.mark.parametrize("vocab,t,top_k,top_p", [(30011, 1.0, 0, 0.9), (30011, 0.7, 50, 1.0), (30011, 1.3, 700, 0.95), (30011, 1.0, 1, 1.0),
+                                                 (1003, 0.8, 5, 0.5), (128256, 0.9, 0, 0.999), (128256, 1.0, 40000, 1.0), (97, 1.0, 200, 0.3)])
+def test_sample_ranked_follows_the_reference_rule(ops, vocab, t, top_k, top_p):
+    """Top-k and nucleus draws on the device against the rule in float64: flat rows (a nucleus of most of the vocabulary),
+    peaked rows, coarse logits with many equal probabilities, every logit -inf, a suppressed maximum. A draw may differ
+    only where the target lies within rounding of a boundary of the cumulated mass, and then by a neighbour."""
+    g = torch.Generator().manual_seed(vocab + top_k)
+    rows = [torch.randn(vocab, generator=g) * 0.3, torch.randn(vocab, generator=g) * 6, torch.round(torch.randn(vocab, generator=g) * 2) / 2,
+            torch.full((vocab,), float("-inf")), torch.randn(vocab, generator=g) * 3]
+    banned = [-1, -1, -1, -1, int(rows[4].argmax())]
+    draws = 256
+    for row, ban in zip(rows, banned):
+        u = torch.rand(draws, generator=g)
+        u[0], u[1] = 0.0, 1.0 - 2.0 ** -24
+        logits = dev(row.expand(draws, vocab).contiguous())
+        out = torch.full((draws,), -7, dtype=torch.int32, device="cuda")
+        ops.sample_ranked(logits, out, dev(torch.full((draws,), t)), dev(u), dev(torch.full((draws,), ban, dtype=torch.int32)),
+                          dev(torch.full((draws,), top_k, dtype=torch.int32)), dev(torch.full((draws,), top_p)))
+        got = out.cpu().long()
+        kept, cum = _ranked_reference(row, t, top_k, top_p, ban)
+        target = u.double() * cum[-1]
+        where = torch.searchsorted(cum, target).clamp(max=len(kept) - 1)
+        want = kept[where]
+        assert int((got < 0).sum()) == 0 and int((got >= vocab).sum()) == 0, "a row was not drawn"
+        if ban >= 0:
+            assert int((got == ban).sum()) == 0, "the suppressed token was drawn"
+        # Where the cumulated mass passes top_p within rounding of it, the cut may fall one entry earlier or later; the
+        # kept mass, and with it every target, then moves by a share of that entry's probability.
+        shift = 0.0
+        if top_p < 1.0 and len(kept) > 1:
+            slack = min(float(cum[-1]) - top_p, top_p - float(cum[-2]))
+            if slack < 1e-5:
+                shift = float(cum[-1] - cum[-2])
+        rank_of = torch.full((vocab,), -1, dtype=torch.long)
+        rank_of[kept] = torch.arange(len(kept))
+        wrong = torch.nonzero(got != want).flatten()
+        assert shift > 0.0 or len(wrong) <= max(2, draws // 50), f"{len(wrong)} of {draws} draws differ from the rule"
+        sorted_p = torch.cat([cum[:1], cum[1:] - cum[:-1]])
+        for i in wrong.tolist():
+            pos = int(rank_of[got[i]])
+            if pos >= 0 and abs(pos - int(where[i])) <= 3 and abs(float(sorted_p[pos] - sorted_p[int(where[i])])) <= 1e-6 * float(sorted_p[pos]):
+                continue         # equal in float32: such entries go by vocabulary order, not by what float64 still tells apart
+            if pos < 0:          # just past the kept set: only where the cut itself lies within rounding
+                assert abs(float(cum[-1]) - top_p) < 1e-5 or int(where[i]) == len(kept) - 1, f"draw {i}: token outside the kept set"
+                continue
+            assert abs(pos - int(where[i])) <= 1 or float(cum[max(pos, int(where[i]))] - cum[min(pos, int(where[i]))]) < 1e-5, \
+                f"draw {i}: rank {pos} instead of {int(where[i])}"
+            edge = min(abs(float(cum[pos] - target[i])), abs(float(cum[max(pos - 1, 0)] - target[i])))
+            assert edge < 1e-5 + shift, f"draw {i}: rank {pos} instead of {int(where[i])}, {edge:.2e} from a boundary (cut slack allows {shift:.2e})"
+
+
+def test_sample_ranked_leaves_other_rows_alone_and_is_exact_on_a_small_distribution(ops):
+    logits = torch.log(torch.tensor([[0.05, 0.4, 0.05, 0.3, 0.2]] * 6))
+    t = torch.tensor([1.0, 1.0, 1.0, 0.0, 1.0, 1.0])
+    top_k = torch.tensor([2, 2, 0, 2, 0, 3], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.6, 1.0, 1.0, 0.95])
+    u = torch.tensor([0.2, 0.8, 0.9, 0.5, 0.5, 0.99])
+    out = torch.full((6,), -7, dtype=torch.int32, device="cuda")
+    ops.sample_ranked(dev(logits), out, dev(t), dev(u), None, dev(top_k), dev(top_p))
+    # rows 0, 1: {1: 0.4, 3: 0.3}, targets 0.14 and 0.56; row 2: nucleus 0.6 keeps {1, 3}, target 0.63; row 3 is greedy and row 4
+    # plain temperature (left alone); row 5: top 3 = {1, 3, 4} = 0.9 < 0.95, target 0.891
+    assert out.tolist() == [1, 3, 3, -7, -7, 4]
+
+
 def test_sample_rows_draws_from_the_softmax(ops):
     g = torch.Generator().manual_seed(12)
     vocab = 1003
