@@ -40,6 +40,8 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-cuda-graphs", action="store_true")
     p.add_argument("--no-chain-steps", action="store_true",
                    help="wait for every decode step's tokens before the next step is launched")
+    p.add_argument("--host-ranking", action="store_true",
+                   help="draw top-k and nucleus rows on the host from their logits instead of on the device")
     p.add_argument("--check-invariants", action="store_true", help="verify the cache manager after every step")
 
 
@@ -63,7 +65,7 @@ def _engine(args):
                    max_batch_seqs=args.max_batch_seqs, max_model_len=args.max_model_len, max_queued=args.max_queued,
                    watermark=args.watermark,
                    chunked_prefill=not args.no_chunked_prefill, prefix_caching=not args.no_prefix_caching,
-                   cuda_graphs=not args.no_cuda_graphs, chain_steps=not args.no_chain_steps,
+                   cuda_graphs=not args.no_cuda_graphs, chain_steps=not args.no_chain_steps, device_ranking=not args.host_ranking,
                    check_invariants=args.check_invariants)
     if args.model:
         return Engine(args.model, **options)

@@ -31,6 +31,7 @@ class EngineConfig:
     check_invariants: bool = False           # verify the cache manager after every step
     cuda_graphs: bool = True                 # replay decode-only steps from captured graphs
     chain_steps: bool = True                 # launch a decode step before the tokens of the one before it are read
+    device_ranking: bool = True              # top-k and nucleus rows are drawn on the device too (False: on the host, from their logits)
     seed: int = 0x57219A3C11FF0042           # base of per-request fallback seeds (crates/stride-engine/src/lib.rs:85)
 
     def __post_init__(self):

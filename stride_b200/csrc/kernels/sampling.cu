@@ -5,8 +5,8 @@
 // float32 (sampler.rs:169-183) and the token is drawn by inverse CDF with the uniform number
 // that the host's generator supplies: the first index, in vocabulary order, at which the
 // running sum of probabilities reaches u * total. A suppressed token (EOS below min_tokens,
-// sampler.rs:81-86) counts as -inf. Top-k and nucleus cuts need a ranking and are done by the
-// host sampler.
+// sampler.rs:81-86) counts as -inf. Rows with a top-k or nucleus cut are drawn by
+// sampling_ranked.cu (or, when the engine is told so, by the host sampler from their logits).
 //
 // The vocabulary is cut into segments of 4096 columns, one CTA per (segment, row), so that a
 // step of a few rows still reads its logits with many SMs. A CTA keeps its segment in shared

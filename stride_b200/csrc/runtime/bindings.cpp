@@ -372,10 +372,19 @@ PYBIND11_MODULE(_runtime, m) {
         .def("rows", &EngineCore::rows)
         .def("prepare_sampling",
              [](EngineCore& c, py::array_t<float, py::array::c_style> temperature, py::array_t<float, py::array::c_style> uniform,
-                py::array_t<int32_t, py::array::c_style> suppress) {
+                py::array_t<int32_t, py::array::c_style> suppress, py::object top_k, py::object top_p) {
                  size_t cap = std::min({size_t(temperature.size()), size_t(uniform.size()), size_t(suppress.size())});
-                 return c.prepare_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
-             })
+                 if (top_k.is_none() || top_p.is_none())
+                     return c.prepare_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
+                 auto k = top_k.cast<py::array_t<int32_t, py::array::c_style>>();
+                 auto p = top_p.cast<py::array_t<float, py::array::c_style>>();
+                 cap = std::min({cap, size_t(k.size()), size_t(p.size())});
+                 return c.prepare_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap,
+                                           k.mutable_data(), p.mutable_data());
+             },
+             py::arg("temperature"), py::arg("uniform"), py::arg("suppress"), py::arg("top_k") = py::none(), py::arg("top_p") = py::none())
+        .def("set_device_ranks", &EngineCore::set_device_ranks)
+        .def_property_readonly("device_ranks", &EngineCore::device_ranks)
         .def("finish_step",
              [](EngineCore& c, py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens, std::vector<int32_t> ranked,
                 py::object ranked_logits, Tick now) {
@@ -395,8 +404,17 @@ PYBIND11_MODULE(_runtime, m) {
         .def("next_batch", [](EngineCore& c) { return &c.next_batch(); }, py::return_value_policy::reference_internal)
         .def("prepare_next_sampling",
              [](EngineCore& c, py::array_t<float, py::array::c_style> temperature, py::array_t<float, py::array::c_style> uniform,
-                py::array_t<int32_t, py::array::c_style> suppress) {
+                py::array_t<int32_t, py::array::c_style> suppress, py::object top_k, py::object top_p) {
                  size_t cap = std::min({size_t(temperature.size()), size_t(uniform.size()), size_t(suppress.size())});
-                 c.prepare_next_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
-             });
+                 if (top_k.is_none() || top_p.is_none()) {
+                     c.prepare_next_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap);
+                     return;
+                 }
+                 auto k = top_k.cast<py::array_t<int32_t, py::array::c_style>>();
+                 auto p = top_p.cast<py::array_t<float, py::array::c_style>>();
+                 cap = std::min({cap, size_t(k.size()), size_t(p.size())});
+                 c.prepare_next_sampling(temperature.mutable_data(), uniform.mutable_data(), suppress.mutable_data(), cap, k.mutable_data(),
+                                         p.mutable_data());
+             },
+             py::arg("temperature"), py::arg("uniform"), py::arg("suppress"), py::arg("top_k") = py::none(), py::arg("top_p") = py::none());
 }

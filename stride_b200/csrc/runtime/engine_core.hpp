@@ -139,6 +139,10 @@ public:
     // True when the open step was launched ahead by chain_step(): the caller only waits for its tokens.
     bool launched_ahead() const { return in_step_ && launched_; }
     uint64_t chained_steps() const { return chained_steps_; }
+    // Whether the device half draws the rows that need a ranking (it then passes top_k / top_p arrays to
+    // prepare_sampling); otherwise finish_step draws them on the host from their logits.
+    void set_device_ranks(bool on) { device_ranks_ = on; }
+    bool device_ranks() const { return device_ranks_; }
     uint64_t dropped_chains() const { return dropped_chains_; }
 
     // ---- between the launch of the open step and the arrival of its tokens: the step after it, launched ahead.
@@ -155,7 +159,7 @@ public:
         if (!batch_->decode_only() || rows_.size() != batch_->num_seqs()) return false;
         for (RequestKey seq : rows_) {
             auto it = live_.find(seq);
-            if (it == live_.end() || it->second.sampler.params().needs_ranking()) return false;
+            if (it == live_.end() || (!device_ranks_ && it->second.sampler.params().needs_ranking())) return false;
         }
         if (scheduled_.decode != rows_) return false;      // rows of ended requests (a chained step being chained again)
         if (!sched_->reserve_chain(scheduled_)) return false;
@@ -173,10 +177,12 @@ public:
     }
 
     // prepare_sampling for the chained step: every request is one token further than its record says.
-    void prepare_next_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity) {
+    void prepare_next_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity, int32_t* top_k = nullptr,
+                               float* top_p = nullptr) {
         if (!next_batch_) throw std::logic_error("no chained step is pending");
         if (next_rows_.size() > capacity) throw std::invalid_argument("more rows than the sampling arrays hold");
-        fill_sampling(next_rows_, 1, temperature, uniform, suppress);
+        if (!fill_sampling(next_rows_, 1, temperature, uniform, suppress, top_k, top_p).empty())
+            throw std::logic_error("a chained step holds a row that the host would have to rank");
     }
 
     const StepBatch& batch() const {
@@ -189,11 +195,12 @@ public:
     // from the request's generator (0 for greedy rows, which draw none) and the token to suppress (-1: none).
     // Returns the rows that need a ranking and are therefore drawn by finish_step from their logits; their
     // device parameters are those of a greedy row.
-    std::vector<int32_t> prepare_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity) {
+    std::vector<int32_t> prepare_sampling(float* temperature, float* uniform, int32_t* suppress, size_t capacity, int32_t* top_k = nullptr,
+                                          float* top_p = nullptr) {
         if (!in_step_) throw std::logic_error("no step is open");
         if (rows_.size() > capacity) throw std::invalid_argument("more rows than the sampling arrays hold");
         if (launched_) throw std::logic_error("the open step was launched ahead with its sampler arrays");
-        return fill_sampling(rows_, 0, temperature, uniform, suppress);
+        return fill_sampling(rows_, 0, temperature, uniform, suppress, top_k, top_p);
     }
 
     // ---- after the launch. `tokens`: one per wanted row, from the device. `ranked_logits`: [ranked rows][vocab]
@@ -271,16 +278,23 @@ private:
         Sampler sampler;
     };
 
-    // `ahead`: tokens that the requests will have produced by then beyond what their records hold.
+    // `ahead`: tokens that the requests will have produced by then beyond what their records hold. With `top_k` and
+    // `top_p` (arrays for a device that ranks: 0 and 1 mean "no cut") a row that needs a ranking gets its temperature,
+    // a uniform number and its cuts like any other; without them it is returned for the host to draw.
     std::vector<int32_t> fill_sampling(const std::vector<RequestKey>& rows, size_t ahead, float* temperature, float* uniform,
-                                       int32_t* suppress) {
+                                       int32_t* suppress, int32_t* top_k = nullptr, float* top_p = nullptr) {
         std::vector<int32_t> ranked;
+        const bool device_ranks = top_k != nullptr && top_p != nullptr;
         for (size_t r = 0; r < rows.size(); ++r) {
             Live& live = live_.at(rows[r]);
             const SamplingParams& p = live.sampler.params();
             size_t generated = records_.at(live.request).tokens.size() + ahead;
             suppress[r] = live.sampler.suppressed_token(generated);
-            if (p.needs_ranking()) {
+            if (device_ranks) {
+                top_k[r] = 0;
+                top_p[r] = 1.f;
+            }
+            if (p.needs_ranking() && !device_ranks) {
                 ranked.push_back(int32_t(r));
                 temperature[r] = 0.f;
                 uniform[r] = 0.f;
@@ -290,6 +304,10 @@ private:
             } else {
                 temperature[r] = p.temperature;
                 uniform[r] = live.sampler.next_uniform();
+                if (p.needs_ranking()) {
+                    top_k[r] = p.top_k ? int32_t(std::min<uint32_t>(*p.top_k, 0x7fffffffu)) : 0;
+                    top_p[r] = p.top_p;
+                }
             }
         }
         return ranked;
@@ -322,6 +340,7 @@ private:
     std::unique_ptr<StepBatch> batch_, next_batch_;
     std::vector<RequestKey> rows_, next_rows_;
     bool in_step_ = false, launched_ = false;
+    bool device_ranks_ = false;      // the device draws top-k and nucleus rows too: such rows do not keep a step from being chained
     uint64_t chained_steps_ = 0, dropped_chains_ = 0;
 };
 

@@ -68,10 +68,11 @@ class _Launch:
 
     def __init__(self, rows: int, device):
         pin = torch.device(device).type == "cuda"
-        self.sample_host = torch.zeros(3 * rows, dtype=torch.float32, pin_memory=pin)
+        self.sample_host = torch.zeros(5 * rows, dtype=torch.float32, pin_memory=pin)
         host = self.sample_host.numpy()
         self.temperature, self.uniform = host[:rows], host[rows:2 * rows]
         self.suppress = host[2 * rows:3 * rows].view(np.int32)
+        self.top_k, self.top_p = host[3 * rows:4 * rows].view(np.int32), host[4 * rows:5 * rows]      # 0 and 1: no cut
         self.tokens_host = torch.zeros(rows, dtype=torch.int32, pin_memory=pin)
         self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
         self.done = torch.cuda.Event()
@@ -120,11 +121,12 @@ class Engine:
         self.extra_eos = tuple(spec.eos_token_ids[1:]) if eos_token_id is None else ()
         self.core = self._rt.EngineCore(self.scheduler, self.eos, list(self.extra_eos), self.cfg.seed & 0xFFFFFFFFFFFFFFFF,
                                         self.cfg.max_queued, self.model.vocab)
+        self.core.set_device_ranks(self.cfg.device_ranking)
         self.now = 0
         self._outputs: dict[int, RequestOutput] = {}    # by request id
         self._seq_of_request: dict[int, int] = {}
         dev = self.model.rt.device
-        self._sample_dev = torch.zeros(3 * row_cap, dtype=torch.float32, device=dev)
+        self._sample_dev = torch.zeros(5 * row_cap, dtype=torch.float32, device=dev)
         self._tokens_dev = torch.zeros(row_cap, dtype=torch.int32, device=dev)
         self._launches = [_Launch(row_cap, dev), _Launch(row_cap, dev)]
         self._turn = 0
@@ -218,19 +220,24 @@ class Engine:
             torch.cuda.nvtx.range_push(f"stride.step tokens={batch.num_tokens} seqs={batch.num_seqs} chained={chained}")
         logits = self.runner.step(batch, token_source=self._tokens_dev[:after.rows] if chained else None)
         cap = self._row_cap
+        cuts = (launch.top_k, launch.top_p) if self.cfg.device_ranking else (None, None)
         if chained:
-            self.core.prepare_next_sampling(launch.temperature, launch.uniform, launch.suppress)
+            self.core.prepare_next_sampling(launch.temperature, launch.uniform, launch.suppress, *cuts)
             launch.ranked = []
         else:
-            launch.ranked = list(self.core.prepare_sampling(launch.temperature, launch.uniform, launch.suppress))
+            launch.ranked = list(self.core.prepare_sampling(launch.temperature, launch.uniform, launch.suppress, *cuts))
         launch.rows, launch.logits = n, logits
         launch.record = {"tokens": batch.num_tokens, "seqs": batch.num_seqs, "rows": n, "decode_only": batch.decode_only,
                          "chained": chained}
         if n:
             dev = self._sample_dev
             dev.copy_(launch.sample_host, non_blocking=True)
-            ops.sample_rows(logits, self._tokens_dev[:n], temperature=dev[:n], uniform=dev[cap:cap + n],
-                            suppress=dev[2 * cap:2 * cap + n].view(torch.int32))
+            suppress = dev[2 * cap:2 * cap + n].view(torch.int32)
+            ops.sample_rows(logits, self._tokens_dev[:n], temperature=dev[:n], uniform=dev[cap:cap + n], suppress=suppress)
+            if self.cfg.device_ranking and ((launch.top_k[:n] > 0).any() or (launch.top_p[:n] < 1.0).any()):
+                # the rows with a top-k or nucleus cut, over what sample_rows wrote for them
+                ops.sample_ranked(logits, self._tokens_dev[:n], dev[:n], dev[cap:cap + n], suppress,
+                                  dev[3 * cap:3 * cap + n].view(torch.int32), dev[4 * cap:4 * cap + n])
             launch.tokens_host[:n].copy_(self._tokens_dev[:n], non_blocking=True)
             self.h2d_bytes += launch.sample_host.numel() * 4
         launch.status_host.copy_(ops.status_tensor(self._tokens_dev.device)[:1], non_blocking=True)

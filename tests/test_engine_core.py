@@ -164,6 +164,60 @@ class CoreLoop:
         return [(e.request, e.token, None if e.reason == rt.FinishReason.NotFinished else e.reason.name) for e in events]
 
 
+def ranked_draw(logits, temperature, uniform, suppress, top_k, top_p) -> int:
+    """What a device that ranks does with a row that has cuts: the host sampler's rule with float32 sums in its order
+    (crates/stride-backend/src/sampler.rs:88-146), the uniform number given instead of drawn."""
+    work = logits.astype(np.float32).copy()
+    if suppress >= 0:
+        work[suppress] = -np.inf
+    if abs(temperature - 1.0) > 1.1920929e-07:
+        work = work / np.float32(temperature)
+    e = np.exp(work - work.max()).astype(np.float32)
+    total = np.float32(0)
+    for v in e:
+        total = np.float32(total + v)
+    probs = (e / total).astype(np.float32)
+    kept = rt.rank_head(probs, top_k if top_k > 0 else None, float(top_p))
+    mass = np.float32(0)
+    for i in kept:
+        mass = np.float32(mass + probs[i])
+    target = np.float32(np.float32(uniform) * mass)
+    for i in kept:
+        target = np.float32(target - probs[i])
+        if target <= 0:
+            return int(i)
+    return int(kept[-1])
+
+
+class DeviceRankLoop(CoreLoop):
+    """``EngineCore`` with a device that draws the ranked rows too: the core hands out their cuts and a uniform number
+    and gets every token back; nothing is ranked in finish_step."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.core.set_device_ranks(True)
+        self.top_k = np.zeros(len(self.temperature), dtype=np.int32)
+        self.top_p = np.ones(len(self.temperature), dtype=np.float32)
+        self.drawn_with_cuts = 0
+
+    def step(self, now):
+        if not self.core.begin_step(now):
+            return None
+        logits = row_logits(self.sched, self.core.batch())
+        ranked = self.core.prepare_sampling(self.temperature, self.uniform, self.suppress, self.top_k, self.top_p)
+        assert list(ranked) == []
+        tokens = []
+        for r in range(len(logits)):
+            t, u, ban, k, p = float(self.temperature[r]), float(self.uniform[r]), int(self.suppress[r]), int(self.top_k[r]), float(self.top_p[r])
+            if t > 0 and (k > 0 or p < 1.0):
+                tokens.append(ranked_draw(logits[r], t, u, ban, k, p))
+                self.drawn_with_cuts += 1
+            else:
+                tokens.append(device_sampler(logits[r], t, u, ban))
+        events = self.core.finish_step(np.array(tokens, dtype=np.int32), [], None, now)
+        return [(e.request, e.token, None if e.reason == rt.FinishReason.NotFinished else e.reason.name) for e in events]
+
+
 def random_params(rng):
     kind = rng.choice(["greedy", "greedy", "temperature", "seeded", "top_k", "top_p", "min_tokens", "stops", "ignore_eos"])
     max_tokens = rng.randint(1, 12)
@@ -228,6 +282,41 @@ def test_core_and_python_loop_agree_event_by_event(seed):
     assert dict(py.sched.metrics()) == dict(core.sched.metrics())
     assert py.cache.stats(0) == core.cache.stats(0)
     assert core.cache.stats(0)["live"] == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_a_device_that_ranks_gets_cuts_and_uniforms_and_changes_no_event(seed):
+    rng = random.Random(100 + seed)
+    pages = rng.choice([14, 18, 40])
+    loops = []
+    for cls in (CoreLoop, DeviceRankLoop):
+        cache, sched = make_scheduler(pages)
+        loops.append(cls(sched, cache))
+    arrivals = sorted((rng.randint(0, 30), [rng.randrange(VOCAB) for _ in range(rng.randint(1, 30))], random_params(random.Random(seed * 77 + i)))
+                      for i in range(14))
+    now, step, idle = 0, 0, 0
+    while step < 400:
+        for at, prompt, params in arrivals:
+            if at == step:
+                ids = []
+                for loop in loops:
+                    try:
+                        ids.append(loop.add_request(prompt, params, now))
+                    except ValueError as e:
+                        ids.append(type(e).__name__)
+                assert ids[0] == ids[1]
+        a, b = (loop.step(now) for loop in loops)
+        assert a == b, f"step {step}: events differ"
+        idle = idle + 1 if a is None else 0
+        now += 1000
+        step += 1
+        if idle > 3 and step > 35:
+            break
+    host, device = loops
+    assert not host.core.has_unfinished() and not device.core.has_unfinished()
+    assert device.core.device_ranks and not host.core.device_ranks
+    if seed == 0:
+        assert sum(l.drawn_with_cuts for l in [device]) > 0, "no row had a cut: the test says nothing"
 
 
 def test_preemption_happens_in_the_small_pools_and_outputs_survive_it():

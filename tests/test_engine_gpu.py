@@ -318,6 +318,24 @@ def test_seeded_sampling(case, dtype):
         assert float(row[tok]) >= third - 0.03 * float(row.abs().max())
 
 
+def test_top_k_and_nucleus_rows_are_drawn_on_the_device_as_on_the_host(case):
+    """The same seeded requests with the cuts applied by the device kernel and by the host sampler (from logits brought
+    back): the same tokens (float32: both see bitwise the same logits, and one uniform number is drawn per token either
+    way), and on the device such rows no longer keep decode steps from being launched ahead."""
+    from stride_b200 import SamplingParams
+    prompts = [case["prompts"][1], case["prompts"][2], case["prompts"][0]]
+    params = [SamplingParams(max_tokens=24, temperature=0.9, top_k=7, seed=21), SamplingParams(max_tokens=24, temperature=1.3, top_p=0.8, seed=22),
+              SamplingParams(max_tokens=24, temperature=1.0, top_k=40, top_p=0.95, seed=23, min_tokens=3)]
+    on_device = engine_for(case, "float32", device_ranking=True)
+    on_host = engine_for(case, "float32", device_ranking=False)
+    a = [o.tokens for o in on_device.generate(prompts, params)]
+    b = [o.tokens for o in on_host.generate(prompts, params)]
+    assert a == b
+    assert all(len(t) == 24 for t in a) and len({tuple(t) for t in a}) == 3
+    assert on_device.metrics()["chained_steps"] > 0 and on_host.metrics()["chained_steps"] == 0
+    assert on_device.d2h_bytes < on_host.d2h_bytes, "the host path brings the logits of ranked rows back"
+
+
 def test_the_command_line(case, tmp_path):
     prompt = case["prompts"][2]
     want = plain.greedy_generate(case["cfg"], case["state"]["float32"], prompt, 6, torch.float64)
