@@ -10,7 +10,8 @@ a batch of 8 requests at a context of 8192 tokens. It prints ONE JSON line:
   weight and the whole cache of the live requests, far more than the L2 holds);
 * ``e2e``: the same through the Python entry point (``Engine.step``): host token
   ids in through pinned memory, scheduling, the step, sampling on the device,
-  token ids back to the host, every step;
+  token ids back to the host, every step (``top_k_top_p``: the same with every row drawn at a
+  temperature with a top-k and a nucleus cut);
 * ``prefill``: one 2,048-token prompt, tokens a second and the fraction of the
   bf16 matrix peak;
 * ``roofline``: bytes the decode step has to read divided by its time, against
@@ -195,7 +196,7 @@ def _rounded(milliseconds: dict, keep: int = 14) -> dict:
     return out
 
 
-def _end_to_end(engine, cfg, batch: int, context: int, steps: int, warmup: int, g) -> dict:
+def _end_to_end(engine, cfg, batch: int, context: int, steps: int, warmup: int, g, cuts: bool = False) -> dict:
     """``steps`` decode steps of ``batch`` requests at ``context`` through ``Engine.step``: the prompts go in as
     host token ids, are prefilled in portions, and every timed step brings host token ids back."""
     import torch
@@ -205,6 +206,8 @@ def _end_to_end(engine, cfg, batch: int, context: int, steps: int, warmup: int, 
     # requests that finish their prompt early keep decoding while the others are still prefilled in portions
     spare = batch * (-(-context // 2048)) + 16
     params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + spare, ignore_eos=True)
+    if cuts:        # every row drawn with a temperature, a top-k and a nucleus cut
+        params = SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=7, max_tokens=warmup + steps + spare, ignore_eos=True)
     ids = [engine.add_request(p, params) for p in prompts]
     while engine.scheduler.num_waiting or any(engine.scheduler.sequence(engine._seq_of_request[i]).state != engine._rt.SeqState.Decoding
                                               for i in ids):
@@ -347,6 +350,8 @@ def run_ours(args) -> dict:
         e2e = _end_to_end(engine, cfg, batch, context, args.steps, max(args.warmup, 3), g)
         if batch != 1 and 1 in point_batches:
             e2e["decode_b1"] = _end_to_end(engine, cfg, 1, context, args.steps, max(args.warmup, 3), g)["value"]
+        # the same with every row drawn at a temperature with a top-k and a nucleus cut (on the device)
+        e2e["top_k_top_p"] = _end_to_end(engine, cfg, batch, context, args.steps, max(args.warmup, 3), g, cuts=True)["value"]
 
     return {
         "metric": f"{SHAPES[args.shape]} decode tok/s at batch {batch}, context {context} (bf16, one B200)",

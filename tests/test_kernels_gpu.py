@@ -375,6 +375,12 @@ def test_sample_ranked_follows_the_reference_rule(ops, vocab, t, top_k, top_p):
         ops.sample_ranked(logits, out, dev(torch.full((draws,), t)), dev(u), dev(torch.full((draws,), ban, dtype=torch.int32)),
                           dev(torch.full((draws,), top_k, dtype=torch.int32)), dev(torch.full((draws,), top_p)))
         got = out.cpu().long()
+        # fewer rows in a launch: clusters of 2, 4 and 8 CTAs a row share the columns; sums are integers, so the draws are the same
+        for fewer in (60, 30, 7):
+            again = torch.full((fewer,), -7, dtype=torch.int32, device="cuda")
+            ops.sample_ranked(logits[:fewer], again, dev(torch.full((fewer,), t)), dev(u[:fewer]), dev(torch.full((fewer,), ban, dtype=torch.int32)),
+                              dev(torch.full((fewer,), top_k, dtype=torch.int32)), dev(torch.full((fewer,), top_p)))
+            assert torch.equal(again.cpu().long(), got[:fewer]), f"{fewer} rows in a launch draw other tokens than 256"
         kept, cum = _ranked_reference(row, t, top_k, top_p, ban)
         target = u.double() * cum[-1]
         where = torch.searchsorted(cum, target).clamp(max=len(kept) - 1)
