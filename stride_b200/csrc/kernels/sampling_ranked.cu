@@ -205,6 +205,10 @@ __device__ __forceinline__ void above(const float* __restrict__ p, int vocab, in
 template <int C, typename Holds>
 __device__ __forceinline__ int search(const float* __restrict__ p, int vocab, int lo, int hi, int count_lo, int count_hi, Mass sum_hi,
                                       Holds holds, int& count_b, Mass& sum_b, int& count_below, Shared& sh, int& turn) {
+    // The first pass puts its thresholds a factor of 16 apart below hi (the largest probability): what a draw keeps
+    // mostly lies within a few such factors of the top, and every later pass then compares only the few columns between
+    // the new bounds with its thresholds. The passes after it cut the range of bit patterns into equal parts.
+    bool by_factors = true;
     while (hi - lo > 1) {
         const long long span = static_cast<long long>(hi) - lo;
         const long long step = span / (kWays + 1) > 0 ? span / (kWays + 1) : 1;
@@ -212,9 +216,14 @@ __device__ __forceinline__ int search(const float* __restrict__ p, int vocab, in
         Mass sum[kWays];
 #pragma unroll
         for (int w = 0; w < kWays; ++w) {
-            const long long t = lo + step * (w + 1);
+            long long t = lo + step * (w + 1);
+            if (by_factors) {
+                t = static_cast<long long>(hi) - (static_cast<long long>(kWays - w) << 25);      // 4 steps of the exponent
+                if (t < lo) t = lo;
+            }
             threshold[w] = static_cast<int>(t < hi ? t : hi - 1);
         }
+        by_factors = false;
         above<C>(p, vocab, lo, hi, count_hi, sum_hi, threshold, count, sum, sh, turn);
         int first = kWays;                    // the first threshold at which it holds
 #pragma unroll
