@@ -133,6 +133,12 @@ __device__ __forceinline__ float reduce_float(float v, bool add, float* s_val, E
     return all;
 }
 
+// A column that may matter to the draw: its probability and its number in the vocabulary.
+struct Candidate {
+    float v;
+    int i;
+};
+
 // Shared state of a CTA that the helpers below use.
 struct Shared {
     int count[kWarps * kWays];
@@ -140,23 +146,71 @@ struct Shared {
     float val[kWarps];
     int scan[kThreads];
     int pick[2];
+    int listed;                          // candidates that asked for a place in the list (more than its capacity: the list is not used)
     Exchange x;
 };
 
+// Where a pass finds the row: in global memory (this CTA takes every C-th group of kThreads columns, or of kThreads
+// packs of four), or, once the columns that can still matter were collected, in the CTA's list in shared memory.
+struct Row {
+    const float* p;                      // [vocab] probabilities
+    int vocab;
+    const Candidate* list;               // the CTA's candidates, or null
+    int listed;
+};
+
+// Calls take(probability, column) for every column of the row that this CTA is in charge of.
+template <int C, typename Take>
+__device__ __forceinline__ void for_columns(const Row& row, Take take) {
+    if (row.list != nullptr) {
+        for (int k = threadIdx.x; k < row.listed; k += kThreads) take(row.list[k].v, row.list[k].i);
+        return;
+    }
+    const int first = (C > 1 ? cluster_rank() : 0) * kThreads + threadIdx.x;
+    constexpr int kStride = C * kThreads;
+    if ((row.vocab & 3) == 0) {          // rows of such a vocabulary start on 16 bytes in the scratch: 16-byte loads, several in flight
+        const float4* p4 = reinterpret_cast<const float4*>(row.p);
+        const int n4 = row.vocab >> 2;
+        constexpr int kInFlight = C >= 4 ? 4 : 8;
+        int i = first;
+        for (; i + (kInFlight - 1) * kStride < n4; i += kInFlight * kStride) {
+            float4 v[kInFlight];
+#pragma unroll
+            for (int k = 0; k < kInFlight; ++k) v[k] = __ldcg(p4 + i + k * kStride);
+#pragma unroll
+            for (int k = 0; k < kInFlight; ++k) {
+                const int col = 4 * (i + k * kStride);
+                take(v[k].x, col); take(v[k].y, col + 1); take(v[k].z, col + 2); take(v[k].w, col + 3);
+            }
+        }
+        for (; i < n4; i += kStride) {
+            const float4 a = __ldcg(p4 + i);
+            take(a.x, 4 * i); take(a.y, 4 * i + 1); take(a.z, 4 * i + 2); take(a.w, 4 * i + 3);
+        }
+    } else {
+        for (int i = first; i < row.vocab; i += kStride) take(__ldcg(row.p + i), i);
+    }
+}
+
 // Count and sum of the probabilities whose bit pattern lies strictly above each of kWays thresholds (ascending, all
 // in [lo, hi)). What lies above hi lies above every threshold and is known (count_hi, sum_hi); what does not lie above
-// lo lies above none: only the columns in between are compared with the thresholds. A CTA of the cluster takes every
-// C-th group of kThreads columns (or of kThreads packs of four).
+// lo lies above none: only the columns in between are compared with the thresholds. With `collect_above` >= -1 the
+// pass also puts every column above that pattern into `collect` (as far as it has room; sh.listed counts them all).
 template <int C>
-__device__ __forceinline__ void above(const float* __restrict__ p, int vocab, int lo, int hi, int count_hi, Mass sum_hi,
-                                      const int (&threshold)[kWays], int (&count)[kWays], Mass (&sum)[kWays], Shared& sh, int& turn) {
+__device__ __forceinline__ void above(const Row& row, int lo, int hi, int count_hi, Mass sum_hi, const int (&threshold)[kWays],
+                                      int (&count)[kWays], Mass (&sum)[kWays], Shared& sh, int& turn, Candidate* collect = nullptr,
+                                      int capacity = 0, int collect_above = 0x7fffffff) {
 #pragma unroll
     for (int w = 0; w < kWays; ++w) {
         count[w] = 0;
         sum[w] = 0;
     }
-    auto take = [&](float v) {
+    for_columns<C>(row, [&](float v, int col) {
         const int bits = __float_as_int(v);
+        if (collect != nullptr && bits > collect_above) {
+            const int place = atomicAdd(&sh.listed, 1);
+            if (place < capacity) collect[place] = Candidate{v, col};
+        }
         if (bits > lo && bits <= hi) {
             const Mass m = mass_of(v);
 #pragma unroll
@@ -167,30 +221,7 @@ __device__ __forceinline__ void above(const float* __restrict__ p, int vocab, in
                 }
             }
         }
-    };
-    const int first = (C > 1 ? cluster_rank() : 0) * kThreads + threadIdx.x;
-    constexpr int kStride = C * kThreads;
-    if ((vocab & 3) == 0) {          // rows of such a vocabulary start on 16 bytes in the scratch: 16-byte loads, several in flight
-        const float4* p4 = reinterpret_cast<const float4*>(p);
-        const int n4 = vocab >> 2;
-        constexpr int kInFlight = C >= 4 ? 4 : 8;
-        int i = first;
-        for (; i + (kInFlight - 1) * kStride < n4; i += kInFlight * kStride) {
-            float4 v[kInFlight];
-#pragma unroll
-            for (int k = 0; k < kInFlight; ++k) v[k] = __ldcg(p4 + i + k * kStride);
-#pragma unroll
-            for (int k = 0; k < kInFlight; ++k) {
-                take(v[k].x); take(v[k].y); take(v[k].z); take(v[k].w);
-            }
-        }
-        for (; i < n4; i += kStride) {
-            const float4 a = __ldcg(p4 + i);
-            take(a.x); take(a.y); take(a.z); take(a.w);
-        }
-    } else {
-        for (int i = first; i < vocab; i += kStride) take(__ldcg(p + i));
-    }
+    });
     reduce_all<C>(count, sum, sh.count, sh.sum, sh.x, turn);
 #pragma unroll
     for (int w = 0; w < kWays; ++w) {
@@ -199,48 +230,65 @@ __device__ __forceinline__ void above(const float* __restrict__ p, int vocab, in
     }
 }
 
+// One step of a search: given what lies above each threshold, the first threshold at which `holds` is true becomes
+// the new hi and the one before it the new lo.
+template <typename Holds>
+__device__ __forceinline__ void narrow(const int (&threshold)[kWays], const int (&count)[kWays], const Mass (&sum)[kWays], Holds holds,
+                                       int& lo, int& hi, int& count_lo, int& count_hi, Mass& sum_hi) {
+    int first = kWays;
+#pragma unroll
+    for (int w = kWays - 1; w >= 0; --w)
+        if (holds(count[w], sum[w])) first = w;
+#pragma unroll
+    for (int w = 0; w < kWays; ++w) {
+        if (w == first) {
+            hi = threshold[w];
+            count_hi = count[w];
+            sum_hi = sum[w];
+        }
+        if (w == first - 1) {
+            lo = threshold[w];
+            count_lo = count[w];
+        }
+    }
+}
+
+// Thresholds a factor of 16 apart below hi (4 steps of the exponent each), none below lo: the first pass of a
+// search. What a draw keeps mostly lies within a few such factors of the largest probability.
+__device__ __forceinline__ void thresholds_by_factors(int lo, int hi, int (&threshold)[kWays]) {
+#pragma unroll
+    for (int w = 0; w < kWays; ++w) {
+        long long t = static_cast<long long>(hi) - (static_cast<long long>(kWays - w) << 25);
+        if (t < lo) t = lo;
+        threshold[w] = static_cast<int>(t < hi ? t : hi - 1);
+    }
+}
+
 // The smallest bit pattern b in (lo, hi] for which `holds(count above b, sum above b)` is true, given that it is true
 // at hi and false at lo (lo may be -1: every probability lies above it) and true for every pattern above the first
-// that makes it true. On return count_b / sum_b are what lies above b, and count_below what lies above b - 1.
+// that makes it true. On return count_b / sum_b are what lies above b, and count_below what lies above b - 1. The
+// first pass goes by factors (unless the caller has made it already), the others cut the range of bit patterns into
+// equal parts.
 template <int C, typename Holds>
-__device__ __forceinline__ int search(const float* __restrict__ p, int vocab, int lo, int hi, int count_lo, int count_hi, Mass sum_hi,
-                                      Holds holds, int& count_b, Mass& sum_b, int& count_below, Shared& sh, int& turn) {
-    // The first pass puts its thresholds a factor of 16 apart below hi (the largest probability): what a draw keeps
-    // mostly lies within a few such factors of the top, and every later pass then compares only the few columns between
-    // the new bounds with its thresholds. The passes after it cut the range of bit patterns into equal parts.
-    bool by_factors = true;
+__device__ __forceinline__ int search(const Row& row, int lo, int hi, int count_lo, int count_hi, Mass sum_hi, bool by_factors, Holds holds,
+                                      int& count_b, Mass& sum_b, int& count_below, Shared& sh, int& turn) {
     while (hi - lo > 1) {
-        const long long span = static_cast<long long>(hi) - lo;
-        const long long step = span / (kWays + 1) > 0 ? span / (kWays + 1) : 1;
         int threshold[kWays], count[kWays];
         Mass sum[kWays];
+        if (by_factors) {
+            thresholds_by_factors(lo, hi, threshold);
+        } else {
+            const long long span = static_cast<long long>(hi) - lo;
+            const long long step = span / (kWays + 1) > 0 ? span / (kWays + 1) : 1;
 #pragma unroll
-        for (int w = 0; w < kWays; ++w) {
-            long long t = lo + step * (w + 1);
-            if (by_factors) {
-                t = static_cast<long long>(hi) - (static_cast<long long>(kWays - w) << 25);      // 4 steps of the exponent
-                if (t < lo) t = lo;
+            for (int w = 0; w < kWays; ++w) {
+                const long long t = lo + step * (w + 1);
+                threshold[w] = static_cast<int>(t < hi ? t : hi - 1);
             }
-            threshold[w] = static_cast<int>(t < hi ? t : hi - 1);
         }
         by_factors = false;
-        above<C>(p, vocab, lo, hi, count_hi, sum_hi, threshold, count, sum, sh, turn);
-        int first = kWays;                    // the first threshold at which it holds
-#pragma unroll
-        for (int w = kWays - 1; w >= 0; --w)
-            if (holds(count[w], sum[w])) first = w;
-#pragma unroll
-        for (int w = 0; w < kWays; ++w) {
-            if (w == first) {
-                hi = threshold[w];
-                count_hi = count[w];
-                sum_hi = sum[w];
-            }
-            if (w == first - 1) {
-                lo = threshold[w];
-                count_lo = count[w];
-            }
-        }
+        above<C>(row, lo, hi, count_hi, sum_hi, threshold, count, sum, sh, turn);
+        narrow(threshold, count, sum, holds, lo, hi, count_lo, count_hi, sum_hi);
     }
     count_b = count_hi;
     sum_b = sum_hi;
@@ -252,9 +300,11 @@ template <int C>
 __global__ void __launch_bounds__(kThreads)
 sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_stride, const float* __restrict__ temperature,
                      const float* __restrict__ uniform, const int32_t* __restrict__ suppress, const int32_t* __restrict__ top_k,
-                     const float* __restrict__ top_p, int32_t* __restrict__ out, float* __restrict__ probs) {
+                     const float* __restrict__ top_p, int32_t* __restrict__ out, float* __restrict__ probs, int capacity) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ __align__(16) unsigned char dynamic[];
+    Candidate* list = reinterpret_cast<Candidate*>(dynamic);
     __shared__ Shared sh;
     const int r = blockIdx.x, tid = threadIdx.x;
     const int rank = C > 1 ? static_cast<int>(cluster_rank()) : 0;
@@ -264,13 +314,13 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
     const float p_limit = top_p[r];
     const bool nucleus = p_limit < 1.f;
     if (!(t > 0.f) || (top_k[r] <= 0 && !nucleus)) return;       // not a ranked row (the whole cluster leaves): the other kernel has drawn it
-    const float* row = logits + static_cast<size_t>(r) * row_stride;
+    const float* logit_row = logits + static_cast<size_t>(r) * row_stride;
     float* p = probs + static_cast<size_t>(r) * vocab;
     const int banned = suppress ? suppress[r] : -1;
     const bool scaled = fabsf(t - 1.f) > 1.1920929e-07f;
 
-    // ---- the probabilities, once. Each thread owns the same columns in every pass (packs of four where the row and
-    // the scratch allow 16-byte accesses).
+    // ---- the probabilities: the maximum, the sum of the exponentials, then each probability, written once. Each pass
+    // reads the logits (packs of four where they allow 16-byte accesses); a thread has the same columns in every pass.
     const bool wide = (vocab & 3) == 0 && (row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
     const int groups = wide ? vocab >> 2 : vocab;
     const int first = rank * kThreads + tid;
@@ -279,93 +329,79 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
         v = i == banned ? -INFINITY : v;
         return scaled ? v / t : v;
     };
-    float mine = -INFINITY;
-    for (int gi = first; gi < groups; gi += kStride) {
-        if (wide) {
-            float4 v = reinterpret_cast<const float4*>(row)[gi];
-            v.x = scaled_logit(4 * gi, v.x); v.y = scaled_logit(4 * gi + 1, v.y); v.z = scaled_logit(4 * gi + 2, v.z); v.w = scaled_logit(4 * gi + 3, v.w);
-            reinterpret_cast<float4*>(p)[gi] = v;
-            mine = fmaxf(fmaxf(mine, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
-        } else {
-            const float v = scaled_logit(gi, row[gi]);
-            p[gi] = v;
-            mine = fmaxf(mine, v);
+    auto for_logits = [&](auto&& each) {         // each(column, scaled logit) -> what to write to p[column] (only the last pass writes)
+        for (int gi = first; gi < groups; gi += kStride) {
+            if (wide) {
+                const float4 v = reinterpret_cast<const float4*>(logit_row)[gi];
+                each(4 * gi, scaled_logit(4 * gi, v.x)); each(4 * gi + 1, scaled_logit(4 * gi + 1, v.y));
+                each(4 * gi + 2, scaled_logit(4 * gi + 2, v.z)); each(4 * gi + 3, scaled_logit(4 * gi + 3, v.w));
+            } else {
+                each(gi, scaled_logit(gi, logit_row[gi]));
+            }
         }
-    }
+    };
+    float mine = -INFINITY;
+    for_logits([&](int, float x) { mine = fmaxf(mine, x); });
     const float mx = reduce_float<C>(mine, false, sh.val, sh.x, turn);
-    float pmax;
-    if (!(mx > -INFINITY)) {                 // every logit is -inf: the uniform distribution
-        pmax = 1.f / static_cast<float>(vocab);
-        for (int i = first; i < vocab; i += kStride) p[i] = pmax;
-    } else {
-        // the sum of the exponentials in fixed point too (they are at most 1 each): it does not depend on how the
-        // columns are spread over threads and CTAs, so neither do the probabilities
-        int none[kWays];
-        Mass part[kWays];
+    const bool flat = !(mx > -INFINITY);         // every logit is -inf: the uniform distribution
+    int none[kWays];
+    Mass part[kWays];
+    auto clear = [&]() {
 #pragma unroll
         for (int w = 0; w < kWays; ++w) {
             none[w] = 0;
             part[w] = 0;
         }
-        for (int gi = first; gi < groups; gi += kStride) {
-            if (wide) {
-                float4 v = reinterpret_cast<float4*>(p)[gi];
-                v.x = expf(v.x - mx); v.y = expf(v.y - mx); v.z = expf(v.z - mx); v.w = expf(v.w - mx);
-                reinterpret_cast<float4*>(p)[gi] = v;
-                part[0] += (mass_of(v.x) + mass_of(v.y)) + (mass_of(v.z) + mass_of(v.w));
-            } else {
-                const float e = expf(p[gi] - mx);
-                p[gi] = e;
-                part[0] += mass_of(e);
-            }
-        }
+    };
+    // the sum of the exponentials in fixed point too (they are at most 1 each): it does not depend on how the columns
+    // are spread over threads and CTAs, so neither do the probabilities
+    float sum = static_cast<float>(vocab);
+    if (!flat) {
+        clear();
+        for_logits([&](int, float x) { part[0] += mass_of(expf(x - mx)); });
         reduce_all<C>(none, part, sh.count, sh.sum, sh.x, turn);
-        const float sum = __ull2float_rn(part[0]) * (1.f / 1099511627776.f);
-        float top = 0.f;
-        for (int gi = first; gi < groups; gi += kStride) {
-            if (wide) {
-                float4 v = reinterpret_cast<float4*>(p)[gi];
-                if (sum > 0.f) { v.x /= sum; v.y /= sum; v.z /= sum; v.w /= sum; }
-                reinterpret_cast<float4*>(p)[gi] = v;
-                top = fmaxf(fmaxf(top, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
-            } else {
-                const float q = sum > 0.f ? p[gi] / sum : p[gi];
-                p[gi] = q;
-                top = fmaxf(top, q);
-            }
-        }
-        pmax = reduce_float<C>(top, false, sh.val, sh.x, turn);
+        sum = __ull2float_rn(part[0]) * (1.f / 1099511627776.f);
     }
-    // Threads read other threads' columns from here on (the last pass also other CTAs'); the reductions above and the
-    // barrier below order the writes before those reads.
-    if (C > 1) {
-        cluster_arrive();
-        cluster_wait();
-    } else {
-        __syncthreads();
-    }
+    const float pmax = sum > 0.f ? 1.f / sum : 1.f;           // the probability of a column that holds the maximum: exp(0) / sum
+    clear();
+    for_logits([&](int col, float x) {
+        const float e = flat ? 1.f : expf(x - mx);
+        const float q = sum > 0.f ? e / sum : e;
+        p[col] = q;
+        part[0] += mass_of(q);
+    });
+    reduce_all<C>(none, part, sh.count, sh.sum, sh.x, turn);    // also orders the writes above before what reads them below
+    const Mass whole = part[0];
+    if (tid == 0) sh.listed = 0;
+    __syncthreads();
     const int top_bits = __float_as_int(pmax);
 
     // ---- the value of the last kept entries: the smallest b such that what lies above b fills neither the top-k
     // budget nor the nucleus
     const Mass p_mass = nucleus ? mass_of(p_limit) : ~Mass(0);
-    auto open_budget = [&](int count, Mass sum) { return count < k_limit && sum < p_mass; };
-    int b, count_b, count_below;
-    Mass sum_b;
-    {
+    auto open_budget = [&](int count, Mass sum_above) { return count < k_limit && sum_above < p_mass; };
+    Row row{p, vocab, nullptr, 0};
+    int b = -1, count_b = vocab, count_below = vocab;
+    Mass sum_b = whole;
+    if (!open_budget(vocab, whole)) {            // else the whole vocabulary is kept
+        // The first pass, by factors below the top, also collects what lies within 2^-16 of the top in shared memory:
+        // when the last kept value lies in there (it mostly does), every later pass reads that list instead of the row.
         int threshold[kWays], count[kWays];
-        Mass sum[kWays];
-#pragma unroll
-        for (int w = 0; w < kWays; ++w) threshold[w] = -1;
-        above<C>(p, vocab, -1, 0x7fffffff, 0, 0, threshold, count, sum, sh, turn);      // everything: the whole mass
-        if (open_budget(count[0], sum[0])) {                               // the whole vocabulary is kept
-            b = -1;
-            count_b = count[0];
-            sum_b = sum[0];
-            count_below = count[0];
-        } else {
-            b = search<C>(p, vocab, -1, top_bits, vocab, 0, 0, open_budget, count_b, sum_b, count_below, sh, turn);
+        Mass above_sum[kWays];
+        thresholds_by_factors(-1, top_bits, threshold);
+        const int collect_above = threshold[3];
+        above<C>(row, -1, top_bits, 0, 0, threshold, count, above_sum, sh, turn, list, capacity, collect_above);
+        int lo = -1, hi = top_bits, count_lo = vocab, count_hi = 0;
+        Mass sum_hi = 0;
+        narrow(threshold, count, above_sum, open_budget, lo, hi, count_lo, count_hi, sum_hi);
+        // every CTA of the cluster must take the same way from here on (they meet at the same barriers): the lists
+        // are used when the value lies within them and none of them ran over
+        const float over = reduce_float<C>(sh.listed > capacity ? 1.f : 0.f, false, sh.val, sh.x, turn);
+        if (lo >= collect_above && over == 0.f) {
+            row.list = list;
+            row.listed = sh.listed;
         }
+        b = search<C>(row, lo, hi, count_lo, count_hi, sum_hi, false, open_budget, count_b, sum_b, count_below, sh, turn);
     }
     const Mass m_b = b >= 0 ? mass_of(__int_as_float(b)) : 0;
     int kept_equals = 0;                     // how many of the entries equal to b's value are kept (in vocabulary order)
@@ -385,10 +421,10 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
     const Mass target = static_cast<Mass>(static_cast<double>(uniform[r]) * static_cast<double>(total));
     int w_bits = top_bits, index_among_equals = 1;
     if (target > 0) {
-        auto short_of_target = [&](int, Mass sum) { return sum < target; };
+        auto short_of_target = [&](int, Mass sum_above) { return sum_above < target; };
         int count_w, count_below_w;
         Mass sum_w;
-        w_bits = search<C>(p, vocab, b >= 0 ? b - 1 : -1, top_bits, count_below, 0, 0, short_of_target, count_w, sum_w, count_below_w, sh, turn);
+        w_bits = search<C>(row, b >= 0 ? b - 1 : -1, top_bits, count_below, 0, 0, true, short_of_target, count_w, sum_w, count_below_w, sh, turn);
         const Mass m_w = mass_of(__int_as_float(w_bits));
         const int equals = w_bits == b ? kept_equals : count_below_w - count_w;
         const Mass steps = m_w > 0 ? (target - sum_w + m_w - 1) / m_w : 1;
@@ -396,8 +432,38 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
         index_among_equals = max(index_among_equals, 1);
     }
 
-    // ---- the entry: the index_among_equals-th column, in vocabulary order, whose probability has the pattern w_bits.
-    // Here a thread takes consecutive columns (thread `rank * kThreads + tid` of C * kThreads the chunk of that number).
+    // ---- the entry: the index_among_equals-th column, in vocabulary order, whose probability has the pattern w_bits
+    if (row.list != nullptr) {
+        // from the lists: the smallest column number that has index_among_equals such columns at or below it
+        int lo = -1, hi = vocab - 1;
+        while (hi - lo > 1) {
+            const int step = (hi - lo) / (kWays + 1) > 0 ? (hi - lo) / (kWays + 1) : 1;
+            int threshold[kWays], count[kWays];
+            Mass unused[kWays];
+#pragma unroll
+            for (int w = 0; w < kWays; ++w) {
+                threshold[w] = min(lo + step * (w + 1), hi - 1);
+                count[w] = 0;
+                unused[w] = 0;
+            }
+            for_columns<C>(row, [&](float v, int col) {
+                if (__float_as_int(v) == w_bits) {
+#pragma unroll
+                    for (int w = 0; w < kWays; ++w) count[w] += col <= threshold[w];
+                }
+            });
+            reduce_all<C>(count, unused, sh.count, sh.sum, sh.x, turn);
+            int first_enough = kWays;
+#pragma unroll
+            for (int w = kWays - 1; w >= 0; --w)
+                if (count[w] >= index_among_equals) first_enough = w;
+            if (first_enough < kWays) hi = threshold[first_enough];
+            if (first_enough > 0) lo = threshold[first_enough - 1];
+        }
+        if (rank == 0 && tid == 0) out[r] = hi;
+        return;
+    }
+    // from the row: here a thread takes consecutive columns (thread `rank * kThreads + tid` of C * kThreads the chunk of that number)
     const int chunk = (vocab + kStride - 1) / kStride;
     const int begin = min(first * chunk, vocab), end = min(begin + chunk, vocab);
     int here = 0;
@@ -416,6 +482,7 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
         tell[0] = make_float4(__int_as_float(sh.pick[0]), 0.f, 0.f, 0.f);
         const int parity = exchange<C>(sh.x, turn, tell, 1);
         for (int k = 0; k < rank; ++k) wanted -= __float_as_int(sh.x.slot[parity][k][0].x);
+        __syncthreads();
     }
     if (tid == 0) {
         int before = 0, owner = -1;
@@ -457,15 +524,28 @@ int stride_sample_ranked(const float* logits, int rows, int vocab, long long row
     if (temperature == nullptr || uniform == nullptr || top_k == nullptr || top_p == nullptr || out == nullptr) return STRIDE_BAD_ARGUMENT;
     if (rows == 0) return 0;
     if (probs == nullptr || probs_floats < static_cast<long long>(rows) * vocab) return STRIDE_BAD_ARGUMENT;
+    constexpr int kCapacity = 20480;                                   // candidates a CTA's list holds: 160 KB
+    constexpr int smem = kCapacity * static_cast<int>(sizeof(Candidate));
+    static bool configured[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return STRIDE_BAD_ARGUMENT;
+    if (!configured[device]) {
+        cudaError_t e = cudaFuncSetAttribute(sample_ranked_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_ranked_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_ranked_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(sample_ranked_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured[device] = true;
+    }
     const dim3 block(kThreads);
-#define STRIDE_RANKED(C)                                                                                                          \
-    stride::launch_clusters(sample_ranked_kernel<C>, dim3(rows, 1, C), block, 0, stream, C, logits, vocab, row_stride, temperature, uniform, \
-                            suppress, top_k, top_p, out, probs)
+#define STRIDE_RANKED(C)                                                                                                             \
+    stride::launch_clusters(sample_ranked_kernel<C>, dim3(rows, 1, C), block, smem, stream, C, logits, vocab, row_stride, temperature, uniform, \
+                            suppress, top_k, top_p, out, probs, kCapacity)
     if (rows <= 18) STRIDE_RANKED(8);
     else if (rows <= 37) STRIDE_RANKED(4);
     else if (rows <= 74) STRIDE_RANKED(2);
-    else stride::launch(sample_ranked_kernel<1>, dim3(rows), block, 0, stream, logits, vocab, row_stride, temperature, uniform, suppress, top_k,
-                        top_p, out, probs);
+    else stride::launch(sample_ranked_kernel<1>, dim3(rows), block, smem, stream, logits, vocab, row_stride, temperature, uniform, suppress, top_k,
+                        top_p, out, probs, kCapacity);
 #undef STRIDE_RANKED
     return STRIDE_LAUNCH_STATUS();
 }
