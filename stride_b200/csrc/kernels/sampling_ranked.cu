@@ -7,14 +7,17 @@
 //
 // Nothing is sorted. Probabilities are not negative, so their float32 bit patterns order like the numbers, and the
 // kept set is "everything above a value b, and the first r entries equal to b": b is found by a search over bit
-// patterns, seven thresholds a pass (three bits of the pattern per pass over the row, eleven passes), each pass
-// counting and summing what lies above every threshold. A second search of the same kind finds the value at which
-// the walk ends, and a last pass the entry among equals, by vocabulary order. A row belongs to a thread-block cluster
-// of 1 to 8 CTAs (more CTAs a row when the step has few rows), each with its share of the columns; what a pass
-// counts is added up over the cluster through distributed shared memory. The row's probabilities are written once to scratch and read from L2 afterwards. Sums of probabilities are integers (fixed
-// point), so a draw is reproducible and does not depend on how the columns are spread over threads; they are not
-// the sequential float32 sums of a host that walks a sorted list, so a draw whose target falls within rounding of a
-// boundary may differ from the host sampler's by one entry of the ranking.
+// patterns, seven thresholds a pass (count and mass of what lies above each): the first pass puts them a factor of 16
+// apart below the largest probability, the later ones cut the remaining range of patterns into eight parts. A second
+// search of the same kind finds the value at which the walk ends, and a last step the entry among equals, by
+// vocabulary order. A row belongs to a thread-block cluster of 1 to 8 CTAs (more CTAs a row when the step has few
+// rows), each with its share of the columns; what a pass counts is added up over the cluster through distributed
+// shared memory. The row's probabilities are written once to scratch and read from L2 afterwards; the first pass of
+// the search also collects the columns within 2^-16 of the largest probability in shared memory, and when the last
+// kept value lies among them (peaked rows), every later pass reads that list instead of the row. Sums of probabilities
+// are integers (fixed point), so a draw is reproducible and does not depend on how the columns are spread over threads
+// and CTAs; they are not the sequential float32 sums of a host that walks a sorted list, so a draw whose target
+// falls within rounding of a boundary may differ from the host sampler's by one entry of the ranking.
 #include "common.cuh"
 
 namespace stride {
