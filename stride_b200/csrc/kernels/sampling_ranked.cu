@@ -14,7 +14,8 @@
 // rows), each with its share of the columns; what a pass counts is added up over the cluster through distributed
 // shared memory. The row's probabilities are written once to scratch and read from L2 afterwards; the first pass of
 // the search also collects the columns within 2^-16 of the largest probability in shared memory, and when the last
-// kept value lies among them (peaked rows), every later pass reads that list instead of the row. Sums of probabilities
+// kept value lies among them (peaked rows), every later pass reads that list instead of the row (and when the lists of
+// a cluster fit into one, its first CTA takes them all and finishes the draw alone). Sums of probabilities
 // are integers (fixed point), so a draw is reproducible and does not depend on how the columns are spread over threads
 // and CTAs; they are not the sequential float32 sums of a host that walks a sorted list, so a draw whose target
 // falls within rounding of a boundary may differ from the host sampler's by one entry of the ranking.
@@ -299,6 +300,133 @@ __device__ __forceinline__ int search(const Row& row, int lo, int hi, int count_
     return hi;
 }
 
+// What a draw needs besides the row.
+struct Draw {
+    int vocab, k_limit, top_bits;
+    bool nucleus;
+    Mass p_mass;
+    float u;
+    int32_t* out;
+    const float* p;
+};
+
+// The rest of a draw once the first pass has narrowed the last kept value to (lo, hi] (or found that the whole
+// vocabulary is kept): by the CC CTAs that still take part (`rank` among them).
+template <int CC, typename Budget>
+__device__ __forceinline__ void finish(const Row& row, const Draw& d, bool keep_all, int lo, int hi, int count_lo, int count_hi, Mass sum_hi,
+                                       Mass whole, Budget open_budget, int rank, Shared& sh, int& turn) {
+    const int tid = threadIdx.x;
+    const float* p = d.p;
+    int b = -1, count_b = d.vocab, count_below = d.vocab;
+    Mass sum_b = whole;
+    if (!keep_all) b = search<CC>(row, lo, hi, count_lo, count_hi, sum_hi, false, open_budget, count_b, sum_b, count_below, sh, turn);
+    const Mass m_b = b >= 0 ? mass_of(__int_as_float(b)) : 0;
+    int kept_equals = 0;                     // how many of the entries equal to b's value are kept (in vocabulary order)
+    Mass total = sum_b;
+    if (b >= 0) {
+        const int equals = count_below - count_b;
+        kept_equals = min(equals, d.k_limit - count_b);
+        if (d.nucleus && m_b > 0) {            // the fewest that bring the cumulated mass to top_p
+            const Mass need = (d.p_mass - sum_b + m_b - 1) / m_b;
+            if (need < static_cast<Mass>(kept_equals)) kept_equals = static_cast<int>(need);
+        }
+        kept_equals = max(kept_equals, 1);
+        total = sum_b + static_cast<Mass>(kept_equals) * m_b;
+    }
+
+    // ---- the walk: the value at which the cumulated probability, from the top, reaches the target u * total
+    const Mass target = static_cast<Mass>(static_cast<double>(d.u) * static_cast<double>(total));
+    int w_bits = d.top_bits, index_among_equals = 1;
+    if (target > 0) {
+        auto short_of_target = [&](int, Mass sum_above) { return sum_above < target; };
+        int count_w, count_below_w;
+        Mass sum_w;
+        w_bits = search<CC>(row, b >= 0 ? b - 1 : -1, d.top_bits, count_below, 0, 0, true, short_of_target, count_w, sum_w, count_below_w, sh, turn);
+        const Mass m_w = mass_of(__int_as_float(w_bits));
+        const int equals = w_bits == b ? kept_equals : count_below_w - count_w;
+        const Mass steps = m_w > 0 ? (target - sum_w + m_w - 1) / m_w : 1;
+        index_among_equals = steps < 1 ? 1 : (steps > static_cast<Mass>(equals) ? equals : static_cast<int>(steps));
+        index_among_equals = max(index_among_equals, 1);
+    }
+
+    // ---- the entry: the index_among_equals-th column, in vocabulary order, whose probability has the pattern w_bits
+    if (row.list != nullptr) {
+        // from the lists: the smallest column number that has index_among_equals such columns at or below it
+        int lo = -1, hi = d.vocab - 1;
+        while (hi - lo > 1) {
+            const int step = (hi - lo) / (kWays + 1) > 0 ? (hi - lo) / (kWays + 1) : 1;
+            int threshold[kWays], count[kWays];
+            Mass unused[kWays];
+#pragma unroll
+            for (int w = 0; w < kWays; ++w) {
+                threshold[w] = min(lo + step * (w + 1), hi - 1);
+                count[w] = 0;
+                unused[w] = 0;
+            }
+            for_columns<CC>(row, [&](float v, int col) {
+                if (__float_as_int(v) == w_bits) {
+#pragma unroll
+                    for (int w = 0; w < kWays; ++w) count[w] += col <= threshold[w];
+                }
+            });
+            reduce_all<CC>(count, unused, sh.count, sh.sum, sh.x, turn);
+            int first_enough = kWays;
+#pragma unroll
+            for (int w = kWays - 1; w >= 0; --w)
+                if (count[w] >= index_among_equals) first_enough = w;
+            if (first_enough < kWays) hi = threshold[first_enough];
+            if (first_enough > 0) lo = threshold[first_enough - 1];
+        }
+        if (rank == 0 && tid == 0) *d.out = hi;
+        return;
+    }
+    // from the row: here a thread takes consecutive columns (thread `rank * kThreads + tid` of CC * kThreads the chunk of that number)
+    constexpr int kStride = CC * kThreads;
+    const int first = rank * kThreads + tid;
+    const int chunk = (d.vocab + kStride - 1) / kStride;
+    const int begin = min(first * chunk, d.vocab), end = min(begin + chunk, d.vocab);
+    int here = 0;
+    for (int i = begin; i < end; ++i) here += __float_as_int(__ldcg(p + i)) == w_bits;
+    sh.scan[tid] = here;
+    __syncthreads();
+    int wanted = index_among_equals;         // counted from this CTA's first column on
+    if (CC > 1) {
+        if (tid == 0) {
+            int mine_total = 0;
+            for (int k = 0; k < kThreads; ++k) mine_total += sh.scan[k];
+            sh.pick[0] = mine_total;
+        }
+        __syncthreads();
+        float4 tell[kWays];
+        tell[0] = make_float4(__int_as_float(sh.pick[0]), 0.f, 0.f, 0.f);
+        const int parity = exchange<CC>(sh.x, turn, tell, 1);
+        for (int k = 0; k < rank; ++k) wanted -= __float_as_int(sh.x.slot[parity][k][0].x);
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int before = 0, owner = -1;
+        for (int k = 0; k < kThreads && wanted >= 1; ++k) {
+            if (before + sh.scan[k] >= wanted) {
+                owner = k;
+                sh.pick[1] = wanted - before;
+                break;
+            }
+            before += sh.scan[k];
+        }
+        sh.pick[0] = owner;                  // -1: the entry lies in another CTA's columns
+    }
+    __syncthreads();
+    if (tid == sh.pick[0]) {
+        int left = sh.pick[1];
+        for (int i = begin; i < end; ++i) {
+            if (__float_as_int(__ldcg(p + i)) == w_bits && --left == 0) {
+                *d.out = i;
+                break;
+            }
+        }
+    }
+}
+
 template <int C>
 __global__ void __launch_bounds__(kThreads)
 sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_stride, const float* __restrict__ temperature,
@@ -384,131 +512,60 @@ sample_ranked_kernel(const float* __restrict__ logits, int vocab, long long row_
     const Mass p_mass = nucleus ? mass_of(p_limit) : ~Mass(0);
     auto open_budget = [&](int count, Mass sum_above) { return count < k_limit && sum_above < p_mass; };
     Row row{p, vocab, nullptr, 0};
-    int b = -1, count_b = vocab, count_below = vocab;
-    Mass sum_b = whole;
-    if (!open_budget(vocab, whole)) {            // else the whole vocabulary is kept
-        // The first pass, by factors below the top, also collects what lies within 2^-16 of the top in shared memory:
-        // when the last kept value lies in there (it mostly does), every later pass reads that list instead of the row.
-        int threshold[kWays], count[kWays];
-        Mass above_sum[kWays];
-        thresholds_by_factors(-1, top_bits, threshold);
-        const int collect_above = threshold[3];
-        above<C>(row, -1, top_bits, 0, 0, threshold, count, above_sum, sh, turn, list, capacity, collect_above);
-        int lo = -1, hi = top_bits, count_lo = vocab, count_hi = 0;
-        Mass sum_hi = 0;
-        narrow(threshold, count, above_sum, open_budget, lo, hi, count_lo, count_hi, sum_hi);
-        // every CTA of the cluster must take the same way from here on (they meet at the same barriers): the lists
-        // are used when the value lies within them and none of them ran over
-        const float over = reduce_float<C>(sh.listed > capacity ? 1.f : 0.f, false, sh.val, sh.x, turn);
-        if (lo >= collect_above && over == 0.f) {
-            row.list = list;
-            row.listed = sh.listed;
-        }
-        b = search<C>(row, lo, hi, count_lo, count_hi, sum_hi, false, open_budget, count_b, sum_b, count_below, sh, turn);
-    }
-    const Mass m_b = b >= 0 ? mass_of(__int_as_float(b)) : 0;
-    int kept_equals = 0;                     // how many of the entries equal to b's value are kept (in vocabulary order)
-    Mass total = sum_b;
-    if (b >= 0) {
-        const int equals = count_below - count_b;
-        kept_equals = min(equals, k_limit - count_b);
-        if (nucleus && m_b > 0) {            // the fewest that bring the cumulated mass to top_p
-            const Mass need = (p_mass - sum_b + m_b - 1) / m_b;
-            if (need < static_cast<Mass>(kept_equals)) kept_equals = static_cast<int>(need);
-        }
-        kept_equals = max(kept_equals, 1);
-        total = sum_b + static_cast<Mass>(kept_equals) * m_b;
-    }
-
-    // ---- the walk: the value at which the cumulated probability, from the top, reaches the target u * total
-    const Mass target = static_cast<Mass>(static_cast<double>(uniform[r]) * static_cast<double>(total));
-    int w_bits = top_bits, index_among_equals = 1;
-    if (target > 0) {
-        auto short_of_target = [&](int, Mass sum_above) { return sum_above < target; };
-        int count_w, count_below_w;
-        Mass sum_w;
-        w_bits = search<C>(row, b >= 0 ? b - 1 : -1, top_bits, count_below, 0, 0, true, short_of_target, count_w, sum_w, count_below_w, sh, turn);
-        const Mass m_w = mass_of(__int_as_float(w_bits));
-        const int equals = w_bits == b ? kept_equals : count_below_w - count_w;
-        const Mass steps = m_w > 0 ? (target - sum_w + m_w - 1) / m_w : 1;
-        index_among_equals = steps < 1 ? 1 : (steps > static_cast<Mass>(equals) ? equals : static_cast<int>(steps));
-        index_among_equals = max(index_among_equals, 1);
-    }
-
-    // ---- the entry: the index_among_equals-th column, in vocabulary order, whose probability has the pattern w_bits
-    if (row.list != nullptr) {
-        // from the lists: the smallest column number that has index_among_equals such columns at or below it
-        int lo = -1, hi = vocab - 1;
-        while (hi - lo > 1) {
-            const int step = (hi - lo) / (kWays + 1) > 0 ? (hi - lo) / (kWays + 1) : 1;
-            int threshold[kWays], count[kWays];
-            Mass unused[kWays];
-#pragma unroll
-            for (int w = 0; w < kWays; ++w) {
-                threshold[w] = min(lo + step * (w + 1), hi - 1);
-                count[w] = 0;
-                unused[w] = 0;
-            }
-            for_columns<C>(row, [&](float v, int col) {
-                if (__float_as_int(v) == w_bits) {
-#pragma unroll
-                    for (int w = 0; w < kWays; ++w) count[w] += col <= threshold[w];
-                }
-            });
-            reduce_all<C>(count, unused, sh.count, sh.sum, sh.x, turn);
-            int first_enough = kWays;
-#pragma unroll
-            for (int w = kWays - 1; w >= 0; --w)
-                if (count[w] >= index_among_equals) first_enough = w;
-            if (first_enough < kWays) hi = threshold[first_enough];
-            if (first_enough > 0) lo = threshold[first_enough - 1];
-        }
-        if (rank == 0 && tid == 0) out[r] = hi;
+    const Draw d{vocab, k_limit, top_bits, nucleus, p_mass, uniform[r], out + r, p};
+    if (open_budget(vocab, whole)) {             // the whole vocabulary is kept
+        finish<C>(row, d, true, -1, top_bits, vocab, 0, 0, whole, open_budget, rank, sh, turn);
         return;
     }
-    // from the row: here a thread takes consecutive columns (thread `rank * kThreads + tid` of C * kThreads the chunk of that number)
-    const int chunk = (vocab + kStride - 1) / kStride;
-    const int begin = min(first * chunk, vocab), end = min(begin + chunk, vocab);
-    int here = 0;
-    for (int i = begin; i < end; ++i) here += __float_as_int(__ldcg(p + i)) == w_bits;
-    sh.scan[tid] = here;
-    __syncthreads();
-    int wanted = index_among_equals;         // counted from this CTA's first column on
+    // The first pass, by factors below the top, also collects what lies within 2^-16 of the top in shared memory:
+    // when the last kept value lies in there (it mostly does), every later pass reads that list instead of the row.
+    int threshold[kWays], count[kWays];
+    Mass above_sum[kWays];
+    thresholds_by_factors(-1, top_bits, threshold);
+    const int collect_above = threshold[3];
+    above<C>(row, -1, top_bits, 0, 0, threshold, count, above_sum, sh, turn, list, capacity, collect_above);
+    int lo = -1, hi = top_bits, count_lo = vocab, count_hi = 0;
+    Mass sum_hi = 0;
+    narrow(threshold, count, above_sum, open_budget, lo, hi, count_lo, count_hi, sum_hi);
+    // Every CTA of the cluster must take the same way from here on (they meet at the same barriers). The lists are used
+    // when the value lies within them and none of them ran over; when they fit into one list together, CTA 0 takes them
+    // all and finishes the draw alone, with no more than a block's reduction per pass.
+    int listed_by[kMaxCluster];
+    int listed_total = sh.listed;
+    bool over = sh.listed > capacity;
     if (C > 1) {
-        if (tid == 0) {
-            int mine_total = 0;
-            for (int k = 0; k < kThreads; ++k) mine_total += sh.scan[k];
-            sh.pick[0] = mine_total;
-        }
-        __syncthreads();
         float4 tell[kWays];
-        tell[0] = make_float4(__int_as_float(sh.pick[0]), 0.f, 0.f, 0.f);
+        tell[0] = make_float4(__int_as_float(sh.listed), 0.f, 0.f, 0.f);
         const int parity = exchange<C>(sh.x, turn, tell, 1);
-        for (int k = 0; k < rank; ++k) wanted -= __float_as_int(sh.x.slot[parity][k][0].x);
-        __syncthreads();
-    }
-    if (tid == 0) {
-        int before = 0, owner = -1;
-        for (int k = 0; k < kThreads && wanted >= 1; ++k) {
-            if (before + sh.scan[k] >= wanted) {
-                owner = k;
-                sh.pick[1] = wanted - before;
-                break;
-            }
-            before += sh.scan[k];
-        }
-        sh.pick[0] = owner;                  // -1: the entry lies in another CTA's columns
-    }
-    __syncthreads();
-    if (tid == sh.pick[0]) {
-        int left = sh.pick[1];
-        for (int i = begin; i < end; ++i) {
-            if (__float_as_int(__ldcg(p + i)) == w_bits && --left == 0) {
-                out[r] = i;
-                break;
-            }
+        listed_total = 0;
+        over = false;
+        for (int k = 0; k < C; ++k) {
+            listed_by[k] = __float_as_int(sh.x.slot[parity][k][0].x);
+            over = over || listed_by[k] > capacity;
+            listed_total += min(listed_by[k], capacity);
         }
     }
+    if (lo < collect_above || over) {            // from the row in global memory
+        finish<C>(row, d, false, lo, hi, count_lo, count_hi, sum_hi, whole, open_budget, rank, sh, turn);
+        return;
+    }
+    row.list = list;
+    row.listed = sh.listed;
+    if (C > 1 && listed_total <= capacity) {
+        int offset = 0;
+        for (int k = 0; k < rank; ++k) offset += listed_by[k];
+        if (rank != 0) {
+            for (int k = tid; k < row.listed; k += kThreads)
+                store_cluster_f2(static_cast<uint32_t>(__cvta_generic_to_shared(list + offset + k)), 0, list[k].v, __int_as_float(list[k].i));
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (rank != 0) return;
+        row.listed = listed_total;
+        finish<1>(row, d, false, lo, hi, count_lo, count_hi, sum_hi, whole, open_budget, 0, sh, turn);
+        return;
+    }
+    finish<C>(row, d, false, lo, hi, count_lo, count_hi, sum_hi, whole, open_budget, rank, sh, turn);
 }
 
 }  // namespace ranked
