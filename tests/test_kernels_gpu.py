@@ -246,9 +246,18 @@ def _paged_case(g, dtype, seqs, nq, nkv, hd, page, window=None, spike=None):
             lo, hi = p * page, min(n, (p + 1) * page)
             k_pages[page_id, :, :hi - lo] = k[lo:hi].transpose(0, 1)
             v_pages[page_id, :, :hi - lo] = v[lo:hi].transpose(0, 1)
-        full = plain.causal_attention(q.double(), k.double(), v.double(), hd ** -0.5, window)
+        if ctx > 8192 and window is None:
+            # a long context: the plain formula (python/stride_worker/layers.py:109-149) for the new rows only, on the GPU
+            qn, kd, vd = q[ctx:].double().cuda(), k.double().cuda(), v.double().cuda()
+            group = nq // nkv
+            scores = torch.einsum("tkgd,skd->kgts", qn.view(new, nkv, group, hd), kd) * hd ** -0.5
+            allowed = torch.arange(n, device="cuda")[None, :] <= torch.arange(ctx, n, device="cuda")[:, None]
+            scores = scores.masked_fill(~allowed[None, None], float("-inf"))
+            rows = torch.einsum("kgts,skd->tkgd", torch.softmax(scores, -1), vd).reshape(new, nq, hd).cpu()
+            want_rows.append(rows)
+        else:
+            want_rows.append(plain.causal_attention(q.double(), k.double(), v.double(), hd ** -0.5, window)[ctx:])
         q_rows.append(q[ctx:])
-        want_rows.append(full[ctx:])
         pos_rows += list(range(ctx, n))
         seq_rows += [s] * new
     q_flat = torch.cat(q_rows).reshape(-1, nq * hd)
@@ -1002,16 +1011,16 @@ def test_prefill_attention_on_tcgen05_walks_long_contexts(ops):
     g = torch.Generator().manual_seed(24)
     dtype = torch.bfloat16
     nq, nkv, hd, page = 8, 2, 128, 16
-    seqs = [(6100, 1024), (3333, 515), (0, 700)]
-    q, k_pages, v_pages, table, _seq_of, _pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, None, spike=(None, 2))
-    q_start, q_len, ctx_len = _seq_arrays(seqs)
-    for _ in range(3):
-        out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
-        assert ops.paged_attention_prefill_tc(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
-                                              dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, 0)
-        torch.cuda.synchronize()
-        assert ops.tc_status() == 0
-        close(out, want, dtype)
+    for seqs, repeats in (([(6100, 1024), (3333, 515), (0, 700)], 3), ([(70000, 300), (0, 130)], 1)):       # the second: a thousand key tiles
+        q, k_pages, v_pages, table, _seq_of, _pos, want = _paged_case(g, dtype, seqs, nq, nkv, hd, page, None, spike=(None, 2))
+        q_start, q_len, ctx_len = _seq_arrays(seqs)
+        for _ in range(repeats):
+            out = torch.full((q.shape[0], nq * hd), 5.0, dtype=dtype, device="cuda")
+            assert ops.paged_attention_prefill_tc(dev(q), nq * hd, out, dev(k_pages), dev(v_pages), dev(table), dev(q_start), dev(q_len),
+                                                  dev(ctx_len), len(seqs), nq, nkv, hd, page, hd ** -0.5, 0)
+            torch.cuda.synchronize()
+            assert ops.tc_status() == 0
+            close(out, want, dtype)
 
 
 def test_prefill_attention_on_tcgen05_refuses_odd_page_sizes(ops):
