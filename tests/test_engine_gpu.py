@@ -310,7 +310,7 @@ def test_seeded_sampling(case, dtype):
         assert_greedy(case, dtype, prompt, cold, "a vanishing temperature must pick the maximum")
     ranked = run(temperature=1.0, top_k=2, top_p=0.9, seed=5)
     assert ranked == run(temperature=1.0, top_k=2, top_p=0.9, seed=5) and len(ranked) == 16
-    # the host-ranked path draws from the two most likely tokens only
+    # a draw with top_k 2 (on the device by default) comes from the two most likely tokens only
     logits = plain.forward(case["cfg"], case["state"][dtype], prompt + ranked, torch.float64)
     for i, tok in enumerate(ranked):
         row = logits[len(prompt) - 1 + i]
